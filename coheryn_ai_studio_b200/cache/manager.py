@@ -39,6 +39,8 @@ class _Group:
     entries: List[int]                   # schedule entries that own a slice
     pool: Optional[PagePool] = None      # a face on the book's pool of this group
     tensor: Optional[torch.Tensor] = None
+    k: Optional[List[torch.Tensor]] = None     # per owning entry: [pages + 1, kv heads, page_size, head_dim]
+    v: Optional[List[torch.Tensor]] = None     # ... and the values (their own head size)
 
 
 class _Requests:
@@ -71,32 +73,50 @@ class CacheManager:
         self.page_size, self.num_pages, self.max_requests = page_size, num_pages, max_requests
         self.dtype, self.device = dtype, device
         self.groups: List[_Group] = []
-        self._entry_group: List[Optional[Tuple[int, int]]] = [None] * len(requirements)
-        self._state: Dict[int, torch.Tensor] = {}
+        # A schedule entry asks for one thing or for a tuple of things (a mixer made of several); what
+        # an entry got is kept per (entry, index in its tuple).
+        self._needs: List[Optional[Tuple]] = []
+        self._entry_group: Dict[Tuple[int, int], Tuple[int, int]] = {}
+        self._state: Dict[Tuple[int, int], torch.Tensor] = {}
         self._cache_from = list(cache_from)
         for e, need in enumerate(requirements):
             if need is None:
+                self._needs.append(None)
                 continue
-            if isinstance(need, PagedKV):
-                for gi, g in enumerate(self.groups):
-                    if g.need == need:
-                        self._entry_group[e] = (gi, len(g.entries))
-                        g.entries.append(e)
-                        break
+            several = isinstance(need, (tuple, list))
+            self._needs.append((several, len(need) if several else 1))
+            for c, one in enumerate(need if several else (need,)):
+                if isinstance(one, PagedKV):
+                    for gi, g in enumerate(self.groups):
+                        if g.need == one:
+                            self._entry_group[(e, c)] = (gi, len(g.entries))
+                            g.entries.append(e)
+                            break
+                    else:
+                        self.groups.append(_Group(one, [e]))
+                        self._entry_group[(e, c)] = (len(self.groups) - 1, 0)
+                elif isinstance(one, FixedState):
+                    self._state[(e, c)] = torch.zeros((max_requests,) + tuple(one.shape), dtype=one.dtype,
+                                                      device=device)
                 else:
-                    self.groups.append(_Group(need, [e]))
-                    self._entry_group[e] = (len(self.groups) - 1, 0)
-            elif isinstance(need, FixedState):
-                self._state[e] = torch.zeros((max_requests,) + tuple(need.shape), dtype=need.dtype,
-                                             device=device)
-            else:
-                raise TypeError(f"schedule entry {e}: unknown cache requirement {need!r}")
+                    raise TypeError(f"schedule entry {e}: unknown cache requirement {one!r}")
         # One page more than the pool hands out: page ``num_pages`` belongs to no request and takes
         # the writes of padding rows (a decode batch padded up to a captured width).
         for g in self.groups:
             n = g.need
-            g.tensor = torch.zeros((len(g.entries), 2, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
-                                   dtype=dtype, device=device)
+            if n.v_head_dim is None or n.v_head_dim == n.head_dim:
+                g.tensor = torch.zeros((len(g.entries), 2, num_pages + 1, n.num_kv_heads, page_size, n.head_dim),
+                                       dtype=dtype, device=device)
+                g.k = [g.tensor[i, 0] for i in range(len(g.entries))]
+                g.v = [g.tensor[i, 1] for i in range(len(g.entries))]
+            else:
+                # values of another head size than keys: per entry the keys of all pages, then the values
+                rows = (num_pages + 1) * n.num_kv_heads * page_size
+                g.tensor = torch.zeros((len(g.entries), rows * (n.head_dim + n.v_head_dim)), dtype=dtype, device=device)
+                g.k = [g.tensor[i, :rows * n.head_dim].view(num_pages + 1, n.num_kv_heads, page_size, n.head_dim)
+                       for i in range(len(g.entries))]
+                g.v = [g.tensor[i, rows * n.head_dim:].view(num_pages + 1, n.num_kv_heads, page_size, n.v_head_dim)
+                       for i in range(len(g.entries))]
         reuse = bool(prefix_reuse) and not self._state and all(g.need.window is None for g in self.groups)
         self._lib = host()
         windows, n_groups = _ints([g.need.window or 0 for g in self.groups])
@@ -123,20 +143,28 @@ class CacheManager:
         return bool(self._lib.coheryn_book_prefix_reuse(self._book))
 
     # ------------------------------------------------------------------ views for the model
+    def _one_cache(self, owner: int, c: int, writes: bool) -> Optional[LayerCache]:
+        if (owner, c) in self._state:
+            return LayerCache(kind="state", state=self._state[(owner, c)], writes=writes)
+        if (owner, c) in self._entry_group:
+            gi, idx = self._entry_group[(owner, c)]
+            g = self.groups[gi]
+            return LayerCache(kind="paged", group=gi, page_size=self.page_size, k=g.k[idx], v=g.v[idx], writes=writes)
+        return None
+
     def layer_caches(self) -> List[Optional[LayerCache]]:
         out: List[Optional[LayerCache]] = []
-        for e in range(len(self._entry_group)):
+        for e in range(len(self._needs)):
             src = self._cache_from[e]
             owner = e if src is None else src
-            if owner in self._state:
-                out.append(LayerCache(kind="state", state=self._state[owner], writes=src is None))
-            elif self._entry_group[owner] is not None:
-                gi, idx = self._entry_group[owner]
-                g = self.groups[gi]
-                out.append(LayerCache(kind="paged", group=gi, page_size=self.page_size,
-                                      k=g.tensor[idx, 0], v=g.tensor[idx, 1], writes=src is None))
-            else:
+            need = self._needs[owner]
+            if need is None:
                 out.append(None)
+            elif need[0]:
+                out.append(LayerCache(kind="several", writes=src is None,
+                                      parts=[self._one_cache(owner, c, src is None) for c in range(need[1])]))
+            else:
+                out.append(self._one_cache(owner, 0, src is None))
         return out
 
     @property
@@ -155,7 +183,8 @@ class CacheManager:
 
     def bytes_per_token(self) -> int:
         item = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * len(g.entries) * g.need.num_kv_heads * g.need.head_dim * item for g in self.groups)
+        return sum(len(g.entries) * g.need.num_kv_heads * (g.need.head_dim + (g.need.v_head_dim or g.need.head_dim)) * item
+                   for g in self.groups)
 
     # ------------------------------------------------------------------ requests
     def _key(self, req_id) -> bytes:

@@ -14,6 +14,7 @@ from typing import Any, Callable, Dict, Optional, Tuple
 
 from .qwen2 import (ConfigError, Qwen2Config, qwen2_config_from_gguf, qwen2_gguf_metadata, qwen2_gguf_name_of,
                     qwen2_gguf_tensor_name, qwen2_model_spec, read_config_json)
+from .kapudra import KapudraConfig, kapudra_model_spec
 from .spec import ModelSpec
 
 
@@ -66,8 +67,10 @@ class Architecture:
         spec = self.model_spec(config)
         spec.validate()
         model = DecoderModel(spec, Runtime(torch.bfloat16, torch.device("cpu")))
-        needs = model.cache_requirements()
-        kv_elements = sum(2 * n.num_kv_heads * n.head_dim for n in needs if isinstance(n, PagedKV))
+        needs = []
+        for n in model.cache_requirements():      # a mixer made of several asks for a tuple
+            needs.extend(n if isinstance(n, (tuple, list)) else [n])
+        kv_elements = sum(n.num_kv_heads * (n.head_dim + (n.v_head_dim or n.head_dim)) for n in needs if isinstance(n, PagedKV))
         state_bytes = 0
         for n in needs:
             if isinstance(n, FixedState):
@@ -125,8 +128,10 @@ def registered_architectures() -> Tuple[str, ...]:
 
 def architecture_for(config_object: Dict[str, Any]) -> Architecture:
     archs = config_object.get("architectures")
+    if archs is None and isinstance(config_object.get("architecture"), str):
+        archs = [config_object["architecture"]]       # some designs name theirs under 'architecture'
     if not isinstance(archs, list) or len(archs) != 1 or not isinstance(archs[0], str):
-        raise ConfigError("config.json must name exactly one architecture in 'architectures'")
+        raise ConfigError("config.json must name exactly one architecture in 'architectures' (or 'architecture')")
     try:
         return _ARCHITECTURES[archs[0]]
     except KeyError:
@@ -180,3 +185,4 @@ register_architecture("Qwen2ForCausalLM", Qwen2Config.from_dict, qwen2_model_spe
                       gguf=GgufFace("qwen2", qwen2_config_from_gguf, qwen2_gguf_tensor_name,
                                     qwen2_gguf_metadata, qwen2_gguf_name_of),
                       adapter_id="qwen2-b200-v1")
+register_architecture("Kapudra", KapudraConfig.from_dict, kapudra_model_spec, adapter_id="kapudra-b200-v1")

@@ -9,7 +9,7 @@ below the registry (parts, cache manager, step function, scheduler) sees only th
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, List, Mapping, Optional
+from typing import Any, Dict, List, Mapping, Optional, Tuple
 
 
 @dataclass(frozen=True)
@@ -36,6 +36,9 @@ class LayerSpec:
     arrangement: str
     parts: Mapping[str, PartSpec]
     position: Optional[PartSpec] = None
+    # Slot name -> the component of the checkpoint's tensor names that the slot's part goes by, for an
+    # arrangement whose checkpoints do not all use the same names (None: the arrangement's own).
+    names: Optional[Mapping[str, str]] = None
 
 
 def prenorm_layer(prefix: str, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec,
@@ -47,14 +50,27 @@ def prenorm_layer(prefix: str, mixer: PartSpec, feed_forward: PartSpec, mixer_no
 
 
 @dataclass(frozen=True)
+class StreamInject:
+    """Something added to the residual stream right before a schedule entry runs: the embedding
+    output of the step's tokens once more (``embedding``), and row ``vector[1]`` of the tensor
+    named ``vector[0]`` (a [rows, width] tensor of ``ModelSpec.extra_tensors``)."""
+
+    embedding: bool = False
+    vector: Optional[Tuple[str, int]] = None
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One execution of a layer.  The schedule is a list of these: a layer may be
     named twice (it then runs twice with the same weights, each run with a cache of
     its own), and ``cache_from`` lets an entry read the cache that an EARLIER entry
-    of the schedule wrote instead of owning one."""
+    of the schedule wrote instead of owning one.  ``inject`` is added to the stream
+    before the entry runs (a model that repeats a span of its layers marks the start
+    of each pass this way)."""
 
     layer: int
     cache_from: Optional[int] = None
+    inject: Optional[StreamInject] = None
 
 
 @dataclass(frozen=True)
@@ -75,6 +91,13 @@ class ModelSpec:
     embedding_scale: Optional[float] = None
     logit_scale: Optional[float] = None
     head_bias_name: Optional[str] = None
+    # logits <- cap * tanh(logits / cap), after scale and bias.
+    logit_softcap: Optional[float] = None
+    # True: ``embedding_name``, ``head_name`` and ``final_norm_name`` are the tensors' full names
+    # (no ".weight" is appended).
+    bare_tensor_names: bool = False
+    # Tensors of the model itself (not of a part): full name -> (shape, role, init) as for a TensorSpec.
+    extra_tensors: Mapping[str, Tuple] = field(default_factory=dict)
 
     def validate(self) -> None:
         if not self.layers:
@@ -94,3 +117,9 @@ class ModelSpec:
                     raise ValueError(
                         f"schedule entry {i} reads the cache of entry {e.cache_from}, "
                         "which owns no cache itself")
+            if e.inject is not None and e.inject.vector is not None:
+                name, row = e.inject.vector
+                shape = self.extra_tensors.get(name, (None,))[0]
+                if shape is None or len(shape) != 2 or shape[1] != self.hidden_size or not 0 <= row < shape[0]:
+                    raise ValueError(f"schedule entry {i} adds row {row} of {name!r}, which is not a row of a "
+                                     f"[rows, {self.hidden_size}] tensor of the model")

@@ -9,6 +9,10 @@
 // k = first + warp, first + warp + 4, ...; their (max, sum, accumulator) triples are
 // merged in warp order.  The result therefore depends only on (p, first), never on
 // how the step was cut or batched.
+//
+// Options of other attention designs: values of another head size than keys (`hdv`); a score that
+// loses slopes[h] * (p - key position) (a bias that grows with distance, one slope per query head);
+// an output multiplied by a constant.
 #include "common.cuh"
 
 namespace {
@@ -21,10 +25,11 @@ attention_simple_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ 
                         const T* __restrict__ k_cache, const T* __restrict__ v_cache,
                         const int* __restrict__ block_tables, int max_blocks,
                         const int* __restrict__ token_req, const int* __restrict__ positions, int nh,
-                        int nkv, int hd, int page_size, int window, float scale) {
+                        int nkv, int hd, int hdv, int page_size, int window, float scale,
+                        const float* __restrict__ slopes, float out_scale) {
   extern __shared__ float smem[];
   float* qs = smem;                         // [hd]
-  float* merge_acc = smem + hd;             // [WARPS][hd]
+  float* merge_acc = smem + hd;             // [WARPS][hdv]
   __shared__ float merge_m[WARPS], merge_l[WARPS];
 
   const int t = blockIdx.x, h = blockIdx.y;
@@ -39,6 +44,7 @@ attention_simple_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ 
   for (int d = threadIdx.x; d < hd; d += blockDim.x) qs[d] = co_to_float(qrow[d]);
   __syncthreads();
 
+  const float slope = slopes ? slopes[h] : 0.f;
   float m = -INFINITY, l = 0.f;
   float acc[MAX_PER_LANE];
 #pragma unroll
@@ -46,9 +52,9 @@ attention_simple_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ 
 
   for (int kp = first + warp; kp <= pos; kp += WARPS) {
     const int page = table[kp / page_size];
-    const size_t base = (((size_t)page * nkv + kvh) * page_size + (kp % page_size)) * hd;
-    const T* kr = k_cache + base;
-    const T* vr = v_cache + base;
+    const size_t row = ((size_t)page * nkv + kvh) * page_size + (kp % page_size);
+    const T* kr = k_cache + row * hd;
+    const T* vr = v_cache + row * hdv;
     float dot = 0.f;
 #pragma unroll
     for (int i = 0; i < MAX_PER_LANE; ++i) {
@@ -56,7 +62,7 @@ attention_simple_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ 
       if (d < hd) dot = fmaf(qs[d], co_to_float(kr[d]), dot);
     }
     dot = co_warp_sum(dot);
-    const float s = dot * scale;
+    const float s = dot * scale - slope * (float)(pos - kp);
     const float m_new = fmaxf(m, s);
     const float corr = expf(m - m_new);  // exp(-inf) = 0 on the first key
     const float p = expf(s - m_new);
@@ -64,7 +70,7 @@ attention_simple_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ 
 #pragma unroll
     for (int i = 0; i < MAX_PER_LANE; ++i) {
       const int d = lane + 32 * i;
-      if (d < hd) acc[i] = acc[i] * corr + p * co_to_float(vr[d]);
+      if (d < hdv) acc[i] = acc[i] * corr + p * co_to_float(vr[d]);
     }
     m = m_new;
   }
@@ -72,7 +78,7 @@ attention_simple_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ 
 #pragma unroll
   for (int i = 0; i < MAX_PER_LANE; ++i) {
     const int d = lane + 32 * i;
-    if (d < hd) merge_acc[warp * hd + d] = acc[i];
+    if (d < hdv) merge_acc[warp * hdv + d] = acc[i];
   }
   __syncthreads();
   float M = -INFINITY;
@@ -86,36 +92,48 @@ attention_simple_kernel(const T* __restrict__ q, long q_stride, T* __restrict__ 
     L += merge_l[w] * f[w];
   }
   const float inv = 1.0f / L;
-  T* orow = out + (size_t)t * out_stride + (size_t)h * hd;
-  for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+  T* orow = out + (size_t)t * out_stride + (size_t)h * hdv;
+  for (int d = threadIdx.x; d < hdv; d += blockDim.x) {
     float o = 0.f;
 #pragma unroll
-    for (int w = 0; w < WARPS; ++w) o += merge_acc[w * hd + d] * f[w];
-    orow[d] = co_from_float<T>(o * inv);
+    for (int w = 0; w < WARPS; ++w) o += merge_acc[w * hdv + d] * f[w];
+    orow[d] = co_from_float<T>(o * inv * out_scale);
   }
 }
 }  // namespace
+
+CO_EXPORT int coheryn_attention_simple_ex(const void* q, long q_stride, void* out, long out_stride,
+                                          const void* k_cache, const void* v_cache, int dtype,
+                                          const int* block_tables, int max_blocks, const int* token_req,
+                                          const int* positions, int T, int nh, int nkv, int hd, int hdv, int page_size,
+                                          int window, float scale, const float* slopes, float out_scale,
+                                          cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (hd > 32 * MAX_PER_LANE || hdv > 32 * MAX_PER_LANE || hd < 1 || hdv < 1)
+    CO_FAIL("attention_simple: head sizes %d and %d must lie in 1..%d", hd, hdv, 32 * MAX_PER_LANE);
+  if (nkv <= 0 || nh % nkv != 0) CO_FAIL("attention_simple: %d heads do not group over %d kv heads", nh, nkv);
+  dim3 grid(T, nh);
+  const size_t smem = ((size_t)hd + (size_t)WARPS * hdv) * sizeof(float);
+  if (dtype == CO_F32)
+    attention_simple_kernel<float><<<grid, WARPS * 32, smem, stream>>>(
+        (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_cache, (const float*)v_cache,
+        block_tables, max_blocks, token_req, positions, nh, nkv, hd, hdv, page_size, window, scale, slopes, out_scale);
+  else if (dtype == CO_BF16)
+    attention_simple_kernel<__nv_bfloat16><<<grid, WARPS * 32, smem, stream>>>(
+        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_cache,
+        (const __nv_bfloat16*)v_cache, block_tables, max_blocks, token_req, positions, nh, nkv, hd, hdv,
+        page_size, window, scale, slopes, out_scale);
+  else CO_FAIL("attention_simple: unknown dtype %d", dtype);
+  CO_CHECK_LAUNCH("attention_simple");
+  return 0;
+}
 
 CO_EXPORT int coheryn_attention_simple(const void* q, long q_stride, void* out, long out_stride,
                                        const void* k_cache, const void* v_cache, int dtype,
                                        const int* block_tables, int max_blocks, const int* token_req,
                                        const int* positions, int T, int nh, int nkv, int hd, int page_size,
                                        int window, float scale, cudaStream_t stream) {
-  if (T <= 0) return 0;
-  if (hd > 32 * MAX_PER_LANE) CO_FAIL("attention_simple: head size %d exceeds %d", hd, 32 * MAX_PER_LANE);
-  if (nkv <= 0 || nh % nkv != 0) CO_FAIL("attention_simple: %d heads do not group over %d kv heads", nh, nkv);
-  dim3 grid(T, nh);
-  const size_t smem = (size_t)(1 + WARPS) * hd * sizeof(float);
-  if (dtype == CO_F32)
-    attention_simple_kernel<float><<<grid, WARPS * 32, smem, stream>>>(
-        (const float*)q, q_stride, (float*)out, out_stride, (const float*)k_cache, (const float*)v_cache,
-        block_tables, max_blocks, token_req, positions, nh, nkv, hd, page_size, window, scale);
-  else if (dtype == CO_BF16)
-    attention_simple_kernel<__nv_bfloat16><<<grid, WARPS * 32, smem, stream>>>(
-        (const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_cache,
-        (const __nv_bfloat16*)v_cache, block_tables, max_blocks, token_req, positions, nh, nkv, hd,
-        page_size, window, scale);
-  else CO_FAIL("attention_simple: unknown dtype %d", dtype);
-  CO_CHECK_LAUNCH("attention_simple");
-  return 0;
+  return coheryn_attention_simple_ex(q, q_stride, out, out_stride, k_cache, v_cache, dtype, block_tables, max_blocks,
+                                     token_req, positions, T, nh, nkv, hd, hd, page_size, window, scale, nullptr, 1.0f,
+                                     stream);
 }

@@ -31,6 +31,7 @@ BASE_FLAGS = ["-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "-Xcompil
 CORE_SOURCES = ["runtime.cu", "elementwise.cu", "gemm_simt.cu", "attention_simple.cu",
                 "sampling.cu", "gemm_bf16_small.cu", "gemm_tc.cu", "gemm_tc_few.cu", "seeded_fill.cu", "selftest.cu",
                 "block_runner.cu"]
+RECURRENT_SOURCES = ["recurrent.cu", "runtime.cu"]
 HEADERS = ["common.cuh"]
 
 
@@ -234,9 +235,15 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
                         {"CO_HEAD_DIM": head_dim})
 
 
+def recurrent_library() -> ctypes.CDLL:
+    """The kernels of mixers with a state of fixed size per request (short convolution, gated delta rule,
+    matrix memory), compiled when a model with such a mixer is first run."""
+    return load_library("recurrent", RECURRENT_SOURCES)
+
+
 def build_all(head_dims: Sequence[int] = (16, 32, 64, 128)) -> List[str]:
     """Compile everything ahead of time (no GPU needed)."""
-    paths = [build_host_library(), build_library("core", CORE_SOURCES)]
+    paths = [build_host_library(), build_library("core", CORE_SOURCES), build_library("recurrent", RECURRENT_SOURCES)]
     for hd in head_dims:
         paths.append(build_library(f"attn_hd{hd}", ["attention_bf16.cu", "attention_tc.cu", "runtime.cu"],
                                    {"CO_HEAD_DIM": hd}))

@@ -133,6 +133,15 @@ __device__ __forceinline__ float co_load_any(const void* p, int dtype, size_t i)
   return dtype == CO_F32 ? ((const float*)p)[i] : __bfloat162float(((const __nv_bfloat16*)p)[i]);
 }
 
+// Activations of the gated epilogues, by the code that the products take as their `epilogue`
+// argument: 1 SiLU g / (1 + exp(-g)), 2 the tanh form of GELU 0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))).
+__device__ __forceinline__ float co_gelu_tanh(float g) {
+  return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+}
+__device__ __forceinline__ float co_gate_act(int code, float g) {
+  return code == 2 ? co_gelu_tanh(g) : __fdividef(g, 1.0f + __expf(-g));
+}
+
 __device__ __forceinline__ float co_warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -85,24 +85,72 @@ CO_EXPORT int coheryn_scatter_words(const void* src, const int* rows, void* out,
 }
 
 // ---------------------------------------------------------------------------------
-// Logits of an architecture that scales them or adds a bias: x[r, v] = x[r, v] * scale + bias[v].
+// Logits of an architecture that scales them, adds a bias or caps them:
+// x[r, v] = x[r, v] * scale + bias[v]; with cap > 0 then x = cap * tanh(x / cap).
 // ---------------------------------------------------------------------------------
 __global__ void scale_add_bias_kernel(float* __restrict__ x, long stride, int V, float scale, const void* __restrict__ bias,
-                                      int bias_dtype) {
+                                      int bias_dtype, float cap) {
   co_pdl_launch_dependents();
   co_pdl_wait();
   float* row = x + (size_t)blockIdx.y * stride;
-  for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < V; v += gridDim.x * blockDim.x)
-    row[v] = row[v] * scale + (bias ? co_load_any(bias, bias_dtype, v) : 0.f);
+  for (int v = blockIdx.x * blockDim.x + threadIdx.x; v < V; v += gridDim.x * blockDim.x) {
+    float y = row[v] * scale + (bias ? co_load_any(bias, bias_dtype, v) : 0.f);
+    if (cap > 0.f) y = cap * tanhf(y / cap);
+    row[v] = y;
+  }
+}
+
+CO_EXPORT int coheryn_scale_bias_cap(float* x, long stride, int R, int V, float scale, const void* bias, int bias_dtype,
+                                     float cap, cudaStream_t stream) {
+  if (R <= 0 || V <= 0) return 0;
+  if (R > 65535) CO_FAIL("scale_add_bias: at most 65535 rows, not %d", R);
+  const int blocks = (V + 1023) / 1024 < 64 ? (V + 1023) / 1024 : 64;
+  co_launch(scale_add_bias_kernel, dim3(blocks, R), dim3(256), 0, stream, x, stride, V, scale, bias, bias_dtype, cap);
+  CO_CHECK_LAUNCH("scale_add_bias");
+  return 0;
 }
 
 CO_EXPORT int coheryn_scale_add_bias(float* x, long stride, int R, int V, float scale, const void* bias, int bias_dtype,
                                      cudaStream_t stream) {
-  if (R <= 0 || V <= 0) return 0;
-  if (R > 65535) CO_FAIL("scale_add_bias: at most 65535 rows, not %d", R);
-  const int blocks = (V + 1023) / 1024 < 64 ? (V + 1023) / 1024 : 64;
-  co_launch(scale_add_bias_kernel, dim3(blocks, R), dim3(256), 0, stream, x, stride, V, scale, bias, bias_dtype);
-  CO_CHECK_LAUNCH("scale_add_bias");
+  return coheryn_scale_bias_cap(x, stride, R, V, scale, bias, bias_dtype, 0.f, stream);
+}
+
+// ---------------------------------------------------------------------------------
+// Something added to the float32 stream between two layers of the schedule (a model that runs a span of
+// its layers several times adds its embedding again, and a vector per pass, before each pass):
+// x[t, :] += table[ids[t], :] * scale (when a table is given) + vec[:] (when given).
+// ---------------------------------------------------------------------------------
+template <typename TW>
+__global__ void stream_inject_kernel(float* __restrict__ x, const TW* __restrict__ table, const int* __restrict__ ids,
+                                     float scale, const void* __restrict__ vec, int vec_dtype, int H, int V) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int t = blockIdx.x;
+  const TW* row = nullptr;
+  if (table) {
+    const int id = ids[t];
+    if (id >= 0 && id < V) row = table + (size_t)id * H;     // the embedding kernel has flagged an id outside the table
+  }
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    float y = x[(size_t)t * H + j];
+    if (row) y += co_to_float(row[j]) * scale;
+    if (vec) y += co_load_any(vec, vec_dtype, j);
+    x[(size_t)t * H + j] = y;
+  }
+}
+
+CO_EXPORT int coheryn_stream_inject(float* x, const void* table, int table_dtype, const int* ids, float scale,
+                                    const void* vec, int vec_dtype, int T, int H, int V, cudaStream_t stream) {
+  if (T <= 0 || H <= 0 || (!table && !vec)) return 0;
+  const int threads = H >= 1024 ? 256 : 128;
+  if (table_dtype == CO_F32)
+    co_launch(stream_inject_kernel<float>, dim3(T), dim3(threads), 0, stream, x, (const float*)table, ids, scale, vec, vec_dtype, H, V);
+  else if (table_dtype == CO_BF16)
+    co_launch(stream_inject_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, stream, x, (const __nv_bfloat16*)table, ids, scale, vec,
+              vec_dtype, H, V);
+  else
+    CO_FAIL("stream_inject: unknown table dtype %d", table_dtype);
+  CO_CHECK_LAUNCH("stream_inject");
   return 0;
 }
 
@@ -512,7 +560,7 @@ CO_EXPORT int coheryn_add_parts_rmsnorm(float* resid, const float* parts, int sp
 // silu(g) = g / (1 + exp(-g)) in float32.
 // ---------------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int I, size_t total) {
+__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int I, size_t total, int code) {
   co_pdl_launch_dependents();
   co_pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -520,17 +568,24 @@ __global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, i
     const size_t m = i / I, j = i % I;
     const float g = co_to_float(in[m * 2 * I + 2 * j]);
     const float u = co_to_float(in[m * 2 * I + 2 * j + 1]);
-    out[i] = co_from_float<T>((g / (1.0f + expf(-g))) * u);
+    out[i] = co_from_float<T>((code == 2 ? co_gelu_tanh(g) : g / (1.0f + expf(-g))) * u);
   }
 }
 
+CO_EXPORT int coheryn_act_mul(const void* in, void* out, int dtype, int M, int I, int code, cudaStream_t stream);
 CO_EXPORT int coheryn_silu_mul(const void* in, void* out, int dtype, int M, int I, cudaStream_t stream) {
+  return coheryn_act_mul(in, out, dtype, M, I, 1, stream);
+}
+
+// code: 1 SiLU, 2 the tanh form of GELU (the codes of the products' gated epilogues).
+CO_EXPORT int coheryn_act_mul(const void* in, void* out, int dtype, int M, int I, int code, cudaStream_t stream) {
+  if (code != 1 && code != 2) CO_FAIL("act_mul: unknown activation code %d", code);
   const size_t total = (size_t)M * I;
   if (total == 0) return 0;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-  if (dtype == CO_F32) co_launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (float*)out, I, total);
-  else if (dtype == CO_BF16) co_launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, I, total);
+  if (dtype == CO_F32) co_launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (float*)out, I, total, code);
+  else if (dtype == CO_BF16) co_launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, I, total, code);
   else CO_FAIL("silu_mul: unknown dtype %d", dtype);
   CO_CHECK_LAUNCH("silu_mul");
   return 0;

@@ -39,7 +39,7 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-constexpr int EPI_GATED_SILU = 1;
+constexpr int EPI_GATED_SILU = 1, EPI_GATED_GELU_TANH = 2;
 
 template <int MT, int NT>
 __global__ void __launch_bounds__(512)
@@ -146,9 +146,9 @@ gemm_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
       v0 += red[wi * E + base];
       v1 += red[wi * E + base + 32];
     }
-    if (epilogue == EPI_GATED_SILU) {
+    if (epilogue != 0) {
       // rows (n, n+1) = (gate_j, up_j), j = n / 2
-      const float r = (v0 / (1.0f + __expf(-v0))) * v1;
+      const float r = (epilogue == EPI_GATED_GELU_TANH ? co_gelu_tanh(v0) : v0 / (1.0f + __expf(-v0))) * v1;
       const size_t o = (size_t)m * ldo + (n >> 1);
       if (out_dtype == CO_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(r);
       else ((float*)out)[o] = r;
@@ -321,8 +321,8 @@ CO_EXPORT int coheryn_gemm_bf16_small(const void* x, const void* w, const void* 
   if (M > 64) CO_FAIL("gemm_bf16_small: M = %d exceeds 64", M);
   if (K <= 0 || (K & 7) || (ldx & 7)) CO_FAIL("gemm_bf16_small: K = %d and the row stride %ld must be multiples of 8", K, ldx);
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_small: operands must be 16-byte aligned");
-  if (epilogue == 1 && (N & 1)) CO_FAIL("gemm_bf16_small: gated epilogue needs an even number of rows");
-  if (epilogue != 0 && epilogue != 1) CO_FAIL("gemm_bf16_small: unknown epilogue %d", epilogue);
+  if (epilogue != 0 && (N & 1)) CO_FAIL("gemm_bf16_small: gated epilogue needs an even number of rows");
+  if (epilogue < 0 || epilogue > EPI_GATED_GELU_TANH) CO_FAIL("gemm_bf16_small: unknown epilogue %d", epilogue);
   // Rows per CTA: as many as keep at least ~2 CTAs per SM (148 SMs); more rows per CTA
   // mean fewer re-reads of x through L2.  The warps of a CTA split K (a function of K
   // alone, so the order of summation never depends on M or N).

@@ -78,6 +78,7 @@ CO_EXPORT int coheryn_gemm_simt(const void* x, int x_dtype, const void* w, int w
   if (x_dtype == CO_F32 && w_dtype == CO_F32 && out_dtype == CO_F32) LAUNCH(float, float, float);
   else if (x_dtype == CO_BF16 && w_dtype == CO_BF16 && out_dtype == CO_BF16) LAUNCH(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
   else if (x_dtype == CO_BF16 && w_dtype == CO_BF16 && out_dtype == CO_F32) LAUNCH(__nv_bfloat16, __nv_bfloat16, float);
+  else if (x_dtype == CO_F32 && w_dtype == CO_BF16 && out_dtype == CO_F32) LAUNCH(float, __nv_bfloat16, float);   // a float32 intermediate times a stored weight
   else CO_FAIL("gemm_simt: unsupported dtypes x=%d w=%d out=%d", x_dtype, w_dtype, out_dtype);
 #undef LAUNCH
   CO_CHECK_LAUNCH("gemm_simt");

@@ -38,7 +38,7 @@ struct Smem {
 // (4 KB, 1024-byte aligned) in the 128-byte swizzle of the output tensor map, and lane 0 sends
 // the 32 x 64 box.  Rows and columns beyond the tensor are clipped by the copy.
 // bias_chunk: the bias of the chunk's first accumulator column (or null).
-__device__ __forceinline__ void store_chunk_tma(unsigned tmem_chunk, const float* bias_chunk, bool gated,
+__device__ __forceinline__ void store_chunk_tma(unsigned tmem_chunk, const float* bias_chunk, int gated,
                                                 unsigned char* stage, const CUtensorMap* map_out, int out_col,
                                                 int out_row, int lane) {
   uint4 pk[8];
@@ -52,8 +52,8 @@ __device__ __forceinline__ void store_chunk_tma(unsigned tmem_chunk, const float
       for (int j = 0; j < 16; j += 2) {
         const float g0 = __uint_as_float(r[2 * j]), u0 = __uint_as_float(r[2 * j + 1]);
         const float g1 = __uint_as_float(r[2 * j + 2]), u1 = __uint_as_float(r[2 * j + 3]);
-        h[q * 8 + (j >> 1)] = __floats2bfloat162_rn(__fdividef(g0, 1.0f + __expf(-g0)) * u0,
-                                                    __fdividef(g1, 1.0f + __expf(-g1)) * u1);
+        h[q * 8 + (j >> 1)] = __floats2bfloat162_rn(co_gate_act(gated, g0) * u0,
+                                                    co_gate_act(gated, g1) * u1);
       }
     }
   } else {
@@ -172,7 +172,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     if (waited && tma_out && !partial) {
       // bfloat16 output through shared memory and TMA stores: every MMA is complete, so the
       // stages are free and serve as the staging area (two 4 KB chunks per warp).
-      const bool gated = epilogue == EPI_GATED_SILU;
+      const int gated = epilogue;   // 0, or the gate's activation code
       const int step = gated ? 128 : 64;
       unsigned char* stage = tiles + quarter * 8192;
       int chunk = 0;
@@ -204,14 +204,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           }
           continue;
         }
-        if (epilogue == EPI_GATED_SILU) {
+        if (epilogue != EPI_PLAIN) {
           // columns (2j, 2j+1) = (gate_j, up_j): 16 outputs per 32 columns
           const int oc = (n0 + c0) >> 1;
           float v[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
-            v[j] = __fdividef(g, 1.0f + __expf(-g)) * u;
+            v[j] = co_gate_act(epilogue, g) * u;
           }
           const int n_out = N >> 1;
           if (out_dtype == CO_BF16) {
@@ -276,14 +276,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 // One 32-column piece of an accumulator row: bias or gate, conversion, store.
 __device__ __forceinline__ void store_piece(const unsigned (&r)[32], int row, int nc, const float* bias_piece,
                                             void* __restrict__ out, int out_dtype, int N, long ldo, int epilogue) {
-  if (epilogue == EPI_GATED_SILU) {
+  if (epilogue != EPI_PLAIN) {
     // columns (2j, 2j+1) = (gate_j, up_j): 16 outputs per 32 columns
     const int oc = nc >> 1, n_out = N >> 1;
     float v[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
-      v[j] = __fdividef(g, 1.0f + __expf(-g)) * u;
+      v[j] = co_gate_act(epilogue, g) * u;
     }
     if (out_dtype == CO_BF16) {
       __nv_bfloat16* p = (__nv_bfloat16*)out + (size_t)row * ldo + oc;
@@ -351,8 +351,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
       v0 += p[0];
       if (has1) v1 += p[1];
     }
-    if (epilogue == EPI_GATED_SILU) {
-      const float r = __fdividef(v0, 1.0f + __expf(-v0)) * v1;
+    if (epilogue != EPI_PLAIN) {
+      const float r = co_gate_act(epilogue, v0) * v1;
       const size_t o = (size_t)m * ldo + (n >> 1);
       if (out_dtype == CO_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(r);
       else ((float*)out)[o] = r;
@@ -686,7 +686,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       }
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (tma_out) {
-        const bool gated = epilogue == EPI_GATED_SILU;
+        const int gated = epilogue;   // 0, or the gate's activation code
         const int step = gated ? 128 : 64;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += step, ++chunk) {
@@ -743,8 +743,8 @@ int launch_tc(const CUtensorMap& mx, const CUtensorMap& mw, const void* bias, in
   // bfloat16 output leaves through shared memory and TMA stores where whole chunks of 64 output
   // columns divide the tile.
   CUtensorMap mo = mx;
-  const int tma_out = !(partial && splits > 1) && BN % (epilogue == EPI_GATED_SILU ? 128 : 64) == 0 &&
-                      make_out_map(&mo, out, out_dtype, M, epilogue == EPI_GATED_SILU ? N / 2 : N, ldo) ? 1 : 0;
+  const int tma_out = !(partial && splits > 1) && BN % (epilogue != EPI_PLAIN ? 128 : 64) == 0 &&
+                      make_out_map(&mo, out, out_dtype, M, epilogue != EPI_PLAIN ? N / 2 : N, ldo) ? 1 : 0;
   auto kernel = gemm_tc_kernel<BN, STAGES>;
   constexpr int smem = Smem<BN, STAGES>::TOTAL;
   static bool configured = false;
@@ -835,7 +835,7 @@ int launch_tc_pair(const CUtensorMap& mx, const CUtensorMap& mw, const void* bia
   const long tiles = (long)((N + BN - 1) / BN) * ((M + 2 * BM - 1) / (2 * BM));
   const int pairs = (int)(tiles < slots ? tiles : slots);
   CUtensorMap mo = mx;
-  const int tma_out = make_out_map(&mo, out, out_dtype, M, epilogue == EPI_GATED_SILU ? N / 2 : N, ldo) ? 1 : 0;
+  const int tma_out = make_out_map(&mo, out, out_dtype, M, epilogue != EPI_PLAIN ? N / 2 : N, ldo) ? 1 : 0;
   cudaError_t le = co_launch_cluster(2, kernel, dim3(2 * pairs), dim3(192), (size_t)smem, stream, mx, mw, mo, tma_out, bias, bias_dtype,
                                      out, out_dtype, M, N, K, ldo, epilogue, status);
   if (le != cudaSuccess) CO_FAIL("gemm_tc_pair: launch failed: %s", cudaGetErrorString(le));
@@ -919,8 +919,8 @@ CO_EXPORT int coheryn_gemm_bf16_tc(const void* x, const void* w, const void* bia
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (ldx & 7)) CO_FAIL("gemm_bf16_tc: K = %d and the row stride %ld must be multiples of 8", K, ldx);
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_tc: operands must be 16-byte aligned");
-  if (epilogue == 1 && (N & 1)) CO_FAIL("gemm_bf16_tc: gated epilogue needs an even number of rows");
-  if (epilogue != 0 && epilogue != 1) CO_FAIL("gemm_bf16_tc: unknown epilogue %d", epilogue);
+  if (epilogue != 0 && (N & 1)) CO_FAIL("gemm_bf16_tc: gated epilogue needs an even number of rows");
+  if (epilogue < 0 || epilogue > 2) CO_FAIL("gemm_bf16_tc: unknown epilogue %d", epilogue);
   if (status && pair_suits(M, N))
     return coheryn_gemm_bf16_tc_pair(x, w, bias, bias_dtype, out, out_dtype, M, N, K, ldx, ldo, epilogue, status, stream);
   const int bn = tile_width(M, N);
@@ -985,8 +985,8 @@ CO_EXPORT int coheryn_gemm_bf16_tc_pair(const void* x, const void* w, const void
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (ldx & 7)) CO_FAIL("gemm_bf16_tc_pair: K = %d and the row stride %ld must be multiples of 8", K, ldx);
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_tc_pair: operands must be 16-byte aligned");
-  if (epilogue == 1 && (N & 1)) CO_FAIL("gemm_bf16_tc_pair: gated epilogue needs an even number of rows");
-  if (epilogue != 0 && epilogue != 1) CO_FAIL("gemm_bf16_tc_pair: unknown epilogue %d", epilogue);
+  if (epilogue != 0 && (N & 1)) CO_FAIL("gemm_bf16_tc_pair: gated epilogue needs an even number of rows");
+  if (epilogue < 0 || epilogue > 2) CO_FAIL("gemm_bf16_tc_pair: unknown epilogue %d", epilogue);
   if (!status) CO_FAIL("gemm_bf16_tc_pair: a status word is required");
   CUtensorMap mx, mw;
   if (!make_map(&mx, x, M, K, ldx, BM) || !make_map(&mw, w, N, K, K, 128))

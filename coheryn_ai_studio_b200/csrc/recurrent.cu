@@ -1,0 +1,479 @@
+// Mixers that carry a state of fixed size per request instead of keys and values per position:
+//
+//   * a short causal convolution over time per channel, followed by SiLU, whose last taps-1 inputs are state;
+//   * the gated delta rule: per head a matrix S [key channels, value channels] with a decay per key channel,
+//       S <- diag(g_t) S;  u = beta_t (v_t - S^T k_t);  S <- S + k_t u^T;  o_t = S^T q_t;
+//   * the stabilised matrix memory (mLSTM): per head S, a normaliser n and a running maximum m of the log gates,
+//       m_t = max(f_t + m_{t-1}, i_t);  a = exp(f_t + m_{t-1} - m_t);  b = exp(i_t - m_t);
+//       S <- a S + b k_t v_t^T;  n <- a n + b k_t;  o_t = S^T q_t / (max(|n . q_t|, exp(-m_t)) + 1e-6);
+//   * the RMS norm per head with a weight and a sigmoid gate that follows both.
+//
+// A step is a batch of requests, each bringing a run of consecutive tokens (cu_q[r] .. cu_q[r+1]) that continues
+// from the request's state slot (state_slots[r]).  Everything that enters a recurrence is float32: the inputs are
+// the float32 outputs of the projections, gates and decays are computed here, the state lives in float32.  The
+// scan kernels give one CTA a (request, head): a thread owns one value channel, i.e. one column of S, in
+// registers, so the three updates of a token need no exchange between threads; the per-token vectors (q, k,
+// decays, gates) of a chunk of tokens are staged and prepared in shared memory by the whole CTA.  A token's result
+// depends on the state and the tokens before it only, in an order of operations that is the same however the
+// sequence was cut into steps.
+#include "common.cuh"
+
+namespace {
+
+constexpr int MAX_TAPS = 16;
+
+__device__ __forceinline__ float rc_sigmoid(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float rc_softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
+__device__ __forceinline__ void rc_store(void* out, int dtype, size_t i, float v) {
+  if (dtype == CO_BF16) ((__nv_bfloat16*)out)[i] = __float2bfloat16_rn(v);
+  else ((float*)out)[i] = v;
+}
+
+// ---------------------------------------------------------------------------------
+// y[t, c] = silu(sum_j taps[c, j] * x[t - (n-1) + j, c]); inputs before the step's first token of a request come
+// from its state [n-1, C] (oldest first), which holds zeros for a request that has just been admitted.
+// ---------------------------------------------------------------------------------
+__global__ void short_conv_silu_kernel(const float* __restrict__ x, long ldx, float* __restrict__ y, long ldy,
+                                       const void* __restrict__ taps, int taps_dtype, int n, int C,
+                                       const float* __restrict__ state, long state_stride,
+                                       const int* __restrict__ token_req, const int* __restrict__ cu_q,
+                                       const int* __restrict__ state_slots, int T) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)T * C) return;
+  const int t = (int)(idx / C), c = (int)(idx % C);
+  const int r = token_req[t];
+  const int start = cu_q[r];
+  const int i = t - start;
+  const float* st = state + (size_t)state_slots[r] * state_stride;
+  float acc = 0.f;
+  for (int j = 0; j < n; ++j) {
+    const int p = i - (n - 1) + j;
+    const float xv = p >= 0 ? x[(size_t)(start + p) * ldx + c] : st[(size_t)(n - 1 + p) * C + c];
+    acc = fmaf(co_load_any(taps, taps_dtype, (size_t)c * n + j), xv, acc);
+  }
+  y[(size_t)t * ldy + c] = acc / (1.0f + expf(-acc));
+}
+
+// The state after the step: the last n-1 inputs of each request, taken from the step's rows and, where the
+// step brought fewer than n-1 tokens, from the old state.
+__global__ void short_conv_state_kernel(const float* __restrict__ x, long ldx, int n, int C, float* __restrict__ state,
+                                        long state_stride, const int* __restrict__ cu_q,
+                                        const int* __restrict__ state_slots, int B) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (size_t)B * C) return;
+  const int r = (int)(idx / C), c = (int)(idx % C);
+  const int start = cu_q[r], len = cu_q[r + 1] - start;
+  if (len <= 0) return;
+  float* st = state + (size_t)state_slots[r] * state_stride;
+  float keep[MAX_TAPS];
+  for (int s = 0; s < n - 1; ++s) {
+    const int p = len - (n - 1) + s;
+    keep[s] = p >= 0 ? x[(size_t)(start + p) * ldx + c] : st[(size_t)(n - 1 + p) * C + c];
+  }
+  for (int s = 0; s < n - 1; ++s) st[(size_t)s * C + c] = keep[s];
+}
+
+// ---------------------------------------------------------------------------------
+// What both scans share: the output of a chunk of tokens (os [CT][dvp], one head) is divided by its root mean
+// square over the value channels, multiplied by a weight and by the sigmoid of a gate's pre-activation, and
+// written in the output's dtype.  A warp takes a token.
+// ---------------------------------------------------------------------------------
+struct HeadOut {
+  void* out; int out_dtype; long ldo;          // [T, heads * dv]
+  const void* weight; int weight_dtype;        // [dv] shared by the heads (weight_stride 0) or [heads * dv]
+  int weight_stride;
+  const float* gate; long ldg;                 // pre-activations [T, heads * dv]
+  float eps, out_scale;
+};
+
+__device__ __forceinline__ void head_out_chunk(const HeadOut& E, const float* os, int dvp, int dv, int nt, int row0, int h) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  for (int i = warp; i < nt; i += warps) {
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) ss = fmaf(os[i * dvp + c], os[i * dvp + c], ss);
+    ss = co_warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)dv + E.eps);
+    const size_t row = (size_t)(row0 + i);
+    for (int c = lane; c < dv; c += 32) {
+      const float w = co_load_any(E.weight, E.weight_dtype, (size_t)h * E.weight_stride + c);
+      const float g = rc_sigmoid(E.gate[row * E.ldg + (size_t)h * dv + c]);
+      rc_store(E.out, E.out_dtype, row * E.ldo + (size_t)h * dv + c, os[i * dvp + c] * inv * w * g * E.out_scale);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Gated delta rule.
+// ---------------------------------------------------------------------------------
+struct DeltaIn {
+  const float* q; const float* k; const float* v; long ld_qkv;   // after convolution and SiLU: [T, kv_heads*dk], .., [T, heads*dv]
+  const float* beta; long ld_beta;                               // pre-activation of beta [T, heads]
+  const float* step; long ld_step;                               // pre-activation of the step size [T, heads*dk] (bias not added)
+  const void* step_bias; int step_bias_dtype;                    // [heads*dk]
+  const void* rate_log; int rate_log_dtype;                      // [heads]: decay = exp(-exp(rate_log) * softplus(step + bias))
+  float* state; long state_stride;                               // per slot: S [heads, dk, dv]
+  const int* cu_q; const int* state_slots;
+  int heads, kv_heads, dk, dv;
+};
+
+template <int DK, int CT>
+__global__ void __launch_bounds__(256) gated_delta_scan_kernel(DeltaIn P, HeadOut E) {
+  extern __shared__ __align__(16) float smem[];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int r = blockIdx.x, h = blockIdx.y, col = threadIdx.x;
+  const int dk = P.dk, dv = P.dv, dvp = blockDim.x;
+  const int start = P.cu_q[r], len = P.cu_q[r + 1] - start;
+  if (len <= 0) return;
+  const int g = h / (P.heads / P.kv_heads);
+  float* qs = smem;                    // [CT][DK]
+  float* ks = qs + CT * DK;            // [CT][DK]
+  float* gs = ks + CT * DK;            // [CT][DK]
+  float* vs = gs + CT * DK;            // [CT][dvp]
+  float* os = vs + CT * dvp;           // [CT][dvp]
+  float* betas = os + CT * dvp;        // [CT]
+  float* S_state = P.state + (size_t)P.state_slots[r] * P.state_stride + (size_t)h * dk * dv;
+  float S[DK];
+#pragma unroll
+  for (int d = 0; d < DK; ++d) S[d] = (d < dk && col < dv) ? S_state[(size_t)d * dv + col] : 0.f;
+  const float rate = expf(co_load_any(P.rate_log, P.rate_log_dtype, h));
+  const float q_scale = 1.0f / sqrtf((float)dk);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+
+  for (int c0 = 0; c0 < len; c0 += CT) {
+    const int nt = min(CT, len - c0), row0 = start + c0;
+    for (int e = threadIdx.x; e < nt * DK; e += blockDim.x) {
+      const int i = e / DK, d = e % DK;
+      const size_t row = (size_t)(row0 + i);
+      float qv = 0.f, kv = 0.f, gv = 1.f;
+      if (d < dk) {
+        qv = P.q[row * P.ld_qkv + (size_t)g * dk + d];
+        kv = P.k[row * P.ld_qkv + (size_t)g * dk + d];
+        const float z = P.step[row * P.ld_step + (size_t)h * dk + d] + co_load_any(P.step_bias, P.step_bias_dtype, (size_t)h * dk + d);
+        gv = expf(-rate * rc_softplus(z));
+      }
+      qs[e] = qv; ks[e] = kv; gs[e] = gv;
+    }
+    for (int e = threadIdx.x; e < nt * dvp; e += blockDim.x) {
+      const int i = e / dvp, c = e % dvp;
+      vs[e] = c < dv ? P.v[(size_t)(row0 + i) * P.ld_qkv + (size_t)h * dv + c] : 0.f;
+    }
+    if (threadIdx.x < nt) betas[threadIdx.x] = rc_sigmoid(P.beta[(size_t)(row0 + threadIdx.x) * P.ld_beta + h]);
+    __syncthreads();
+    // q and k become unit vectors (q also divided by sqrt(dk)): a warp per token
+    for (int i = warp; i < nt; i += warps) {
+      float sq = 0.f, sk = 0.f;
+      for (int d = lane; d < DK; d += 32) { sq = fmaf(qs[i * DK + d], qs[i * DK + d], sq); sk = fmaf(ks[i * DK + d], ks[i * DK + d], sk); }
+      sq = co_warp_sum(sq); sk = co_warp_sum(sk);
+      const float iq = q_scale / sqrtf(sq + 1e-6f), ik = 1.0f / sqrtf(sk + 1e-6f);
+      for (int d = lane; d < DK; d += 32) { qs[i * DK + d] *= iq; ks[i * DK + d] *= ik; }
+    }
+    __syncthreads();
+    for (int i = 0; i < nt; ++i) {
+      const float4* k4 = reinterpret_cast<const float4*>(ks + i * DK);
+      const float4* g4 = reinterpret_cast<const float4*>(gs + i * DK);
+      const float4* q4 = reinterpret_cast<const float4*>(qs + i * DK);
+      float dot = 0.f;
+#pragma unroll
+      for (int d = 0; d < DK / 4; ++d) {
+        const float4 gg = g4[d], kk = k4[d];
+        S[4 * d] *= gg.x; S[4 * d + 1] *= gg.y; S[4 * d + 2] *= gg.z; S[4 * d + 3] *= gg.w;
+        dot = fmaf(S[4 * d], kk.x, dot); dot = fmaf(S[4 * d + 1], kk.y, dot);
+        dot = fmaf(S[4 * d + 2], kk.z, dot); dot = fmaf(S[4 * d + 3], kk.w, dot);
+      }
+      const float u = betas[i] * (vs[i * dvp + col] - dot);
+      float o = 0.f;
+#pragma unroll
+      for (int d = 0; d < DK / 4; ++d) {
+        const float4 kk = k4[d], qq = q4[d];
+        S[4 * d] = fmaf(kk.x, u, S[4 * d]); S[4 * d + 1] = fmaf(kk.y, u, S[4 * d + 1]);
+        S[4 * d + 2] = fmaf(kk.z, u, S[4 * d + 2]); S[4 * d + 3] = fmaf(kk.w, u, S[4 * d + 3]);
+        o = fmaf(S[4 * d], qq.x, o); o = fmaf(S[4 * d + 1], qq.y, o);
+        o = fmaf(S[4 * d + 2], qq.z, o); o = fmaf(S[4 * d + 3], qq.w, o);
+      }
+      os[i * dvp + col] = o;
+    }
+    __syncthreads();
+    head_out_chunk(E, os, dvp, dv, nt, row0, h);
+    __syncthreads();
+  }
+  if (col < dv) {
+#pragma unroll
+    for (int d = 0; d < DK; ++d)
+      if (d < dk) S_state[(size_t)d * dv + col] = S[d];
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Stabilised matrix memory.
+// ---------------------------------------------------------------------------------
+struct MemoryIn {
+  const float* q; const float* k; const float* v; long ld;       // projections [T, heads*dk], .., [T, heads*dv] (one row stride)
+  const float* gi; const float* gf; long ld_gate;                // pre-activations of the input and forget gates [T, heads]
+  const void* bias_i; const void* bias_f; int bias_dtype;        // [heads]
+  float cap;                                                     // gates are capped: cap * tanh(z / cap)
+  float* state; long state_stride;                               // per slot: S [heads, dk, dv], n [heads, dk], m [heads]
+  const int* cu_q; const int* state_slots;
+  int heads, dk, dv;
+};
+
+template <int DK, int CT>
+__global__ void __launch_bounds__(256) matrix_memory_scan_kernel(MemoryIn P, HeadOut E) {
+  extern __shared__ __align__(16) float smem[];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int r = blockIdx.x, h = blockIdx.y, col = threadIdx.x;
+  const int dk = P.dk, dv = P.dv, dvp = blockDim.x;
+  const int start = P.cu_q[r], len = P.cu_q[r + 1] - start;
+  if (len <= 0) return;
+  float* qs = smem;                    // [CT][DK]
+  float* ks = qs + CT * DK;            // [CT][DK]
+  float* vs = ks + CT * DK;            // [CT][dvp]
+  float* os = vs + CT * dvp;           // [CT][dvp]
+  float* li = os + CT * dvp;           // [CT] log input gate, then b = exp(i - m)
+  float* lf = li + CT;                 // [CT] log forget gate, then a = exp(f + m' - m)
+  float* den = lf + CT;                // [CT]
+  float* slot = P.state + (size_t)P.state_slots[r] * P.state_stride;
+  float* S_state = slot + (size_t)h * dk * dv;
+  float* n_state = slot + (size_t)P.heads * dk * dv + (size_t)h * dk;
+  float* m_state = slot + (size_t)P.heads * dk * dv + (size_t)P.heads * dk + h;
+  float S[DK];
+#pragma unroll
+  for (int d = 0; d < DK; ++d) S[d] = (d < dk && col < dv) ? S_state[(size_t)d * dv + col] : 0.f;
+  constexpr int NJ = (DK + 31) / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float nreg[NJ];                      // warp 0: lane holds n[lane + 32 j]
+  float m = 0.f;
+  if (warp == 0) {
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) nreg[j] = (lane + 32 * j < dk) ? n_state[lane + 32 * j] : 0.f;
+    m = *m_state;
+  }
+  const float q_scale = 1.0f / sqrtf((float)dk);
+  const float bi = co_load_any(P.bias_i, P.bias_dtype, h), bf = co_load_any(P.bias_f, P.bias_dtype, h);
+
+  for (int c0 = 0; c0 < len; c0 += CT) {
+    const int nt = min(CT, len - c0), row0 = start + c0;
+    for (int e = threadIdx.x; e < nt * DK; e += blockDim.x) {
+      const int i = e / DK, d = e % DK;
+      const size_t row = (size_t)(row0 + i);
+      qs[e] = d < dk ? P.q[row * P.ld + (size_t)h * dk + d] * q_scale : 0.f;
+      ks[e] = d < dk ? P.k[row * P.ld + (size_t)h * dk + d] : 0.f;
+    }
+    for (int e = threadIdx.x; e < nt * dvp; e += blockDim.x) {
+      const int i = e / dvp, c = e % dvp;
+      vs[e] = c < dv ? P.v[(size_t)(row0 + i) * P.ld + (size_t)h * dv + c] : 0.f;
+    }
+    if (threadIdx.x < nt) {
+      const size_t row = (size_t)(row0 + threadIdx.x);
+      li[threadIdx.x] = P.cap * tanhf((P.gi[row * P.ld_gate + h] + bi) / P.cap);
+      const float z = P.cap * tanhf((P.gf[row * P.ld_gate + h] + bf) / P.cap);
+      lf[threadIdx.x] = -rc_softplus(-z);          // log sigmoid
+    }
+    __syncthreads();
+    if (warp == 0) {
+      // the scalar part of the recurrence, token by token: maximum, the two factors, normaliser and denominator
+      for (int i = 0; i < nt; ++i) {
+        const float f = lf[i], in = li[i];
+        const float m_new = fmaxf(f + m, in);
+        const float a = expf(f + m - m_new), b = expf(in - m_new);
+        m = m_new;
+        float part = 0.f;
+#pragma unroll
+        for (int j = 0; j < NJ; ++j) {
+          const int d = lane + 32 * j;
+          if (d < DK) {
+            nreg[j] = fmaf(b, ks[i * DK + d], a * nreg[j]);
+            part = fmaf(nreg[j], qs[i * DK + d], part);
+          }
+        }
+        part = co_warp_sum(part);
+        __syncwarp();
+        if (lane == 0) { lf[i] = a; li[i] = b; den[i] = fmaxf(fabsf(part), expf(-m)) + 1e-6f; }
+      }
+    }
+    __syncthreads();
+    for (int i = 0; i < nt; ++i) {
+      const float4* k4 = reinterpret_cast<const float4*>(ks + i * DK);
+      const float4* q4 = reinterpret_cast<const float4*>(qs + i * DK);
+      const float a = lf[i], bv = li[i] * vs[i * dvp + col];
+      float o = 0.f;
+#pragma unroll
+      for (int d = 0; d < DK / 4; ++d) {
+        const float4 kk = k4[d], qq = q4[d];
+        S[4 * d] = fmaf(bv, kk.x, a * S[4 * d]); S[4 * d + 1] = fmaf(bv, kk.y, a * S[4 * d + 1]);
+        S[4 * d + 2] = fmaf(bv, kk.z, a * S[4 * d + 2]); S[4 * d + 3] = fmaf(bv, kk.w, a * S[4 * d + 3]);
+        o = fmaf(S[4 * d], qq.x, o); o = fmaf(S[4 * d + 1], qq.y, o);
+        o = fmaf(S[4 * d + 2], qq.z, o); o = fmaf(S[4 * d + 3], qq.w, o);
+      }
+      os[i * dvp + col] = o / den[i];
+    }
+    __syncthreads();
+    head_out_chunk(E, os, dvp, dv, nt, row0, h);
+    __syncthreads();
+  }
+  if (col < dv) {
+#pragma unroll
+    for (int d = 0; d < DK; ++d)
+      if (d < dk) S_state[(size_t)d * dv + col] = S[d];
+  }
+  if (warp == 0) {
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+      if (lane + 32 * j < dk) n_state[lane + 32 * j] = nreg[j];
+    if (lane == 0) *m_state = m;
+  }
+}
+
+// ---------------------------------------------------------------------------------
+// Queries and keys normalised over the WHOLE projection (all heads at once), keys and values written into
+// cache pages: q_out[t] = q / rms(q) * wq, K[slot] = k / rms(k) * wk, V[slot] = v.  A CTA per token.
+// normalise = 0 copies q and k as they are.
+// ---------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_norm_kv_write_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, long ld,
+                        const void* __restrict__ wq, const void* __restrict__ wk, int w_dtype, float eps, int normalise,
+                        T* __restrict__ q_out, long ldq, const int* __restrict__ slots, T* __restrict__ k_cache,
+                        T* __restrict__ v_cache, int nh, int nkv, int dk, int dv, int page_size) {
+  __shared__ float scratch[33];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const size_t t = blockIdx.x;
+  const int nq = nh * dk, nk = nkv * dk, nv = nkv * dv;
+  const float* qr = q + t * ld;
+  const float* kr = k + t * ld;
+  const float* vr = v + t * ld;
+  float iq = 1.f, ik = 1.f;
+  if (normalise) {
+    float s = 0.f;
+    for (int e = threadIdx.x; e < nq; e += blockDim.x) s = fmaf(qr[e], qr[e], s);
+    iq = 1.0f / sqrtf(co_block_sum(s, scratch) / (float)nq + eps);
+    s = 0.f;
+    for (int e = threadIdx.x; e < nk; e += blockDim.x) s = fmaf(kr[e], kr[e], s);
+    ik = 1.0f / sqrtf(co_block_sum(s, scratch) / (float)nk + eps);
+  }
+  for (int e = threadIdx.x; e < nq; e += blockDim.x)
+    q_out[t * ldq + e] = co_from_float<T>(normalise ? qr[e] * iq * co_load_any(wq, w_dtype, e) : qr[e]);
+  if (!slots) return;
+  const int slot = slots[t];
+  const size_t page = slot / page_size, off = slot % page_size;
+  for (int e = threadIdx.x; e < nk; e += blockDim.x) {
+    const int g = e / dk, d = e % dk;
+    k_cache[((page * nkv + g) * page_size + off) * dk + d] =
+        co_from_float<T>(normalise ? kr[e] * ik * co_load_any(wk, w_dtype, e) : kr[e]);
+  }
+  for (int e = threadIdx.x; e < nv; e += blockDim.x) {
+    const int g = e / dv, d = e % dv;
+    v_cache[((page * nkv + g) * page_size + off) * dv + d] = co_from_float<T>(vr[e]);
+  }
+}
+
+constexpr int chunk_tokens(int DK) { return DK <= 128 ? 16 : 8; }
+
+}  // namespace
+
+CO_EXPORT int coheryn_short_conv_silu(const float* x, long ldx, float* y, long ldy, const void* taps, int taps_dtype, int n,
+                                      int C, float* state, long state_stride, const int* token_req, const int* cu_q,
+                                      const int* state_slots, int T, int B, int update_state, cudaStream_t stream) {
+  if (T <= 0 || C <= 0) return 0;
+  if (n < 1 || n > MAX_TAPS) CO_FAIL("short_conv: 1..%d taps, not %d", MAX_TAPS, n);
+  const size_t total = (size_t)T * C;
+  co_launch(short_conv_silu_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, ldx, y, ldy, taps, taps_dtype, n,
+            C, (const float*)state, state_stride, token_req, cu_q, state_slots, T);
+  CO_CHECK_LAUNCH("short_conv_silu");
+  if (update_state && n > 1) {
+    const size_t per = (size_t)B * C;
+    co_launch(short_conv_state_kernel, dim3((unsigned)((per + 255) / 256)), dim3(256), 0, stream, x, ldx, n, C, state, state_stride,
+              cu_q, state_slots, B);
+    CO_CHECK_LAUNCH("short_conv_state");
+  }
+  return 0;
+}
+
+#define CO_SCAN_CASES(LAUNCH)                                                                   \
+  if (dk <= 16) { LAUNCH(16) } else if (dk <= 32) { LAUNCH(32) } else if (dk <= 48) { LAUNCH(48) } \
+  else if (dk <= 64) { LAUNCH(64) } else if (dk <= 96) { LAUNCH(96) } else if (dk <= 128) { LAUNCH(128) } \
+  else if (dk <= 192) { LAUNCH(192) } else { LAUNCH(256) }
+
+static int scan_shape_ok(const char* name, int heads, int dk, int dv) {
+  if (heads < 1 || dk < 1 || dk > 256 || dv < 1 || dv > 256) {
+    co_set_error("%s: heads %d, key channels %d (1..256), value channels %d (1..256)", name, heads, dk, dv);
+    return 0;
+  }
+  return 1;
+}
+
+CO_EXPORT int coheryn_gated_delta_scan(
+    const float* q, const float* k, const float* v, long ld_qkv, const float* beta, long ld_beta, const float* step,
+    long ld_step, const void* step_bias, int step_bias_dtype, const void* rate_log, int rate_log_dtype, float* state,
+    long state_stride, const int* cu_q, const int* state_slots, int B, int heads, int kv_heads, int dk, int dv, void* out,
+    int out_dtype, long ldo, const void* weight, int weight_dtype, int weight_stride, const float* gate, long ldg, float eps,
+    float out_scale, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (!scan_shape_ok("gated_delta_scan", heads, dk, dv)) return 1;
+  if (kv_heads < 1 || heads % kv_heads) CO_FAIL("gated_delta_scan: %d heads do not group over %d q/k heads", heads, kv_heads);
+  DeltaIn P{q, k, v, ld_qkv, beta, ld_beta, step, ld_step, step_bias, step_bias_dtype, rate_log, rate_log_dtype, state,
+            state_stride, cu_q, state_slots, heads, kv_heads, dk, dv};
+  HeadOut E{out, out_dtype, ldo, weight, weight_dtype, weight_stride, gate, ldg, eps, out_scale};
+  const int threads = (dv + 31) / 32 * 32;
+#define LAUNCH(D)                                                                                              \
+  {                                                                                                            \
+    constexpr int CT = chunk_tokens(D);                                                                        \
+    const size_t smem = ((size_t)3 * CT * D + (size_t)2 * CT * threads + CT) * sizeof(float);                  \
+    auto kern = gated_delta_scan_kernel<D, CT>;                                                                \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+    co_launch_ex(true, kern, dim3(B, heads), dim3(threads), smem, stream, P, E);                               \
+  }
+  CO_SCAN_CASES(LAUNCH)
+#undef LAUNCH
+  CO_CHECK_LAUNCH("gated_delta_scan");
+  return 0;
+}
+
+CO_EXPORT int coheryn_matrix_memory_scan(
+    const float* q, const float* k, const float* v, long ld, const float* gi, const float* gf, long ld_gate,
+    const void* bias_i, const void* bias_f, int bias_dtype, float cap, float* state, long state_stride, const int* cu_q,
+    const int* state_slots, int B, int heads, int dk, int dv, void* out, int out_dtype, long ldo, const void* weight,
+    int weight_dtype, int weight_stride, const float* gate, long ldg, float eps, float out_scale, cudaStream_t stream) {
+  if (B <= 0) return 0;
+  if (!scan_shape_ok("matrix_memory_scan", heads, dk, dv)) return 1;
+  if (!(cap > 0.f)) CO_FAIL("matrix_memory_scan: the gate cap must be positive");
+  MemoryIn P{q, k, v, ld, gi, gf, ld_gate, bias_i, bias_f, bias_dtype, cap, state, state_stride, cu_q, state_slots, heads, dk, dv};
+  HeadOut E{out, out_dtype, ldo, weight, weight_dtype, weight_stride, gate, ldg, eps, out_scale};
+  const int threads = (dv + 31) / 32 * 32;
+#define LAUNCH(D)                                                                                              \
+  {                                                                                                            \
+    constexpr int CT = chunk_tokens(D);                                                                        \
+    const size_t smem = ((size_t)2 * CT * D + (size_t)2 * CT * threads + 3 * CT) * sizeof(float);              \
+    auto kern = matrix_memory_scan_kernel<D, CT>;                                                              \
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+    co_launch_ex(true, kern, dim3(B, heads), dim3(threads), smem, stream, P, E);                               \
+  }
+  CO_SCAN_CASES(LAUNCH)
+#undef LAUNCH
+  CO_CHECK_LAUNCH("matrix_memory_scan");
+  return 0;
+}
+
+CO_EXPORT int coheryn_qk_norm_kv_write(const float* q, const float* k, const float* v, long ld, const void* wq, const void* wk,
+                                       int w_dtype, float eps, int normalise, void* q_out, int dtype, long ldq, const int* slots,
+                                       void* k_cache, void* v_cache, int T, int nh, int nkv, int dk, int dv, int page_size,
+                                       cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (nh < 1 || nkv < 0 || dk < 1 || dv < 1 || page_size < 1) CO_FAIL("qk_norm_kv_write: bad sizes");
+  if (dtype == CO_F32)
+    co_launch(qk_norm_kv_write_kernel<float>, dim3(T), dim3(256), 0, stream, q, k, v, ld, wq, wk, w_dtype, eps, normalise,
+              (float*)q_out, ldq, slots, (float*)k_cache, (float*)v_cache, nh, nkv, dk, dv, page_size);
+  else if (dtype == CO_BF16)
+    co_launch(qk_norm_kv_write_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, q, k, v, ld, wq, wk, w_dtype, eps, normalise,
+              (__nv_bfloat16*)q_out, ldq, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv, dk, dv, page_size);
+  else
+    CO_FAIL("qk_norm_kv_write: unknown dtype %d", dtype);
+  CO_CHECK_LAUNCH("qk_norm_kv_write");
+  return 0;
+}

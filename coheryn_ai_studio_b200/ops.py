@@ -32,6 +32,7 @@ def require_gpu() -> None:
 
 _core = None
 _attn_libs = {}
+_recurrent = None
 
 
 def core():
@@ -54,7 +55,7 @@ def launch_count() -> int:
 def total_launch_count() -> int:
     """Kernel launches made through every library of this package that is loaded."""
     n = launch_count()
-    for lib in _attn_libs.values():
+    for lib in list(_attn_libs.values()) + ([_recurrent] if _recurrent is not None else []):
         n += int(lib.coheryn_launch_count())
     return n
 
@@ -144,16 +145,41 @@ def scatter_words(src: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> N
     _check(lib, lib.coheryn_scatter_words(_ptr(src), _ptr(rows), _ptr(out), c_int(rows.numel()), _stream()))
 
 
-def scale_add_bias(x: torch.Tensor, scale: Optional[float], bias: Optional[torch.Tensor]) -> None:
-    """In place on float32 rows: x = x * scale + bias (either may be absent)."""
+def scale_add_bias(x: torch.Tensor, scale: Optional[float], bias: Optional[torch.Tensor],
+                   softcap: Optional[float] = None) -> None:
+    """In place on float32 rows: x = x * scale + bias (either may be absent); with ``softcap`` c then
+    x = c * tanh(x / c)."""
     _dev(x, bias)
     assert x.dtype == torch.float32 and x.dim() == 2 and x.stride(1) == 1
     if bias is not None:
         assert bias.shape == (x.shape[1],) and bias.is_contiguous()
+    if softcap is not None and not softcap > 0:
+        raise KernelError("a logit cap must be positive")
     lib = core()
-    _check(lib, lib.coheryn_scale_add_bias(_ptr(x), c_long(x.stride(0)), c_int(x.shape[0]), c_int(x.shape[1]),
+    _check(lib, lib.coheryn_scale_bias_cap(_ptr(x), c_long(x.stride(0)), c_int(x.shape[0]), c_int(x.shape[1]),
                                            c_float(1.0 if scale is None else scale), _ptr(bias),
-                                           c_int(_code(bias) if bias is not None else F32), _stream()))
+                                           c_int(_code(bias) if bias is not None else F32),
+                                           c_float(0.0 if softcap is None else softcap), _stream()))
+
+
+def stream_inject(x: torch.Tensor, table: Optional[torch.Tensor], ids: Optional[torch.Tensor], scale: Optional[float],
+                  vector: Optional[torch.Tensor]) -> None:
+    """In place on the float32 stream: x[t] += table[ids[t]] * scale (when a table is given) + vector (when given)."""
+    _dev(x, table, ids, vector)
+    T, H = x.shape
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    V = 0
+    if table is not None:
+        _i32(ids, "ids")
+        assert table.is_contiguous() and table.shape[1] == H and ids.numel() == T
+        V = table.shape[0]
+    if vector is not None:
+        assert vector.shape == (H,) and vector.is_contiguous()
+    lib = core()
+    _check(lib, lib.coheryn_stream_inject(_ptr(x), _ptr(table), c_int(_code(table) if table is not None else F32), _ptr(ids),
+                                          c_float(1.0 if scale is None else scale), _ptr(vector),
+                                          c_int(_code(vector) if vector is not None else F32), c_int(T), c_int(H), c_int(V),
+                                          _stream()))
 
 
 def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
@@ -189,15 +215,16 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
         c_int(H), c_int(1 if (update and delta is not None) else 0), _stream()))
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[m, j] = silu(gate_up[m, 2j]) * gate_up[m, 2j + 1] (gate and up interleaved)."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, code: int = 1) -> None:
+    """out[m, j] = act(gate_up[m, 2j]) * gate_up[m, 2j + 1] (gate and up interleaved); ``code`` names the
+    activation as the gated epilogues do (``GATED_ACTIVATIONS``; 1 = SiLU)."""
     _dev(gate_up, out)
     M, I2 = gate_up.shape
     assert I2 % 2 == 0 and out.shape == (M, I2 // 2) and out.dtype == gate_up.dtype
     assert gate_up.is_contiguous() and out.is_contiguous()
     lib = core()
-    _check(lib, lib.coheryn_silu_mul(_ptr(gate_up), _ptr(out), c_int(_code(out)), c_int(M),
-                                     c_int(I2 // 2), _stream()))
+    _check(lib, lib.coheryn_act_mul(_ptr(gate_up), _ptr(out), c_int(_code(out)), c_int(M),
+                                    c_int(I2 // 2), c_int(code), _stream()))
 
 
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
@@ -345,20 +372,26 @@ def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
 def attention_simple(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                      block_tables: torch.Tensor, token_req: torch.Tensor, positions: torch.Tensor,
                      num_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
-                     window: Optional[int], scale: float) -> None:
+                     window: Optional[int], scale: float, v_head_dim: Optional[int] = None,
+                     slopes: Optional[torch.Tensor] = None, out_scale: float = 1.0) -> None:
     """Causal attention of each token over its request's cache pages (float32 math).
-    ``q`` may be a column slice of a wider buffer (its row stride is honoured)."""
-    _dev(q, out, k_cache, v_cache, block_tables, token_req, positions)
+    ``q`` may be a column slice of a wider buffer (its row stride is honoured).  ``v_head_dim``: values
+    of another head size than keys; ``slopes`` (float32 [heads]): the score of a key at distance d loses
+    slopes[h] * d; ``out_scale`` multiplies the output."""
+    _dev(q, out, k_cache, v_cache, block_tables, token_req, positions, slopes)
     _i32(block_tables, "block_tables"); _i32(token_req, "token_req"); _i32(positions, "positions")
     T = q.shape[0]
-    assert q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == num_heads * head_dim
-    assert k_cache.dtype == q.dtype and out.dtype == q.dtype
+    vd = head_dim if v_head_dim is None else v_head_dim
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == num_heads * head_dim and out.shape[1] == num_heads * vd
+    assert k_cache.dtype == q.dtype and out.dtype == q.dtype and v_cache.dtype == q.dtype
+    if slopes is not None:
+        assert slopes.dtype == torch.float32 and slopes.is_contiguous() and slopes.numel() == num_heads
     lib = core()
-    _check(lib, lib.coheryn_attention_simple(
+    _check(lib, lib.coheryn_attention_simple_ex(
         _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
         c_int(_code(q)), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(token_req),
-        _ptr(positions), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
-        c_int(page_size), c_int(window or 0), c_float(scale), _stream()))
+        _ptr(positions), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(vd),
+        c_int(page_size), c_int(window or 0), c_float(scale), _ptr(slopes), c_float(out_scale), _stream()))
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
@@ -662,6 +695,16 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
                    settled=step.prior_positions_settled)
 
 
+def attention_biased(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
+                     num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, page_size: int,
+                     window: Optional[int], scale: float, slopes: Optional[torch.Tensor], out_scale: float = 1.0) -> None:
+    """Attention of every token of the step over its request's cache pages of ``group`` with a score that loses
+    slopes[h] times the distance, values of their own head size and a scaled output."""
+    attention_simple(q, out, k_cache, v_cache, step.block_tables[group], step.token_req, step.positions, num_heads,
+                     num_kv_heads, head_dim, page_size, window, scale, v_head_dim=v_head_dim, slopes=slopes,
+                     out_scale=out_scale)
+
+
 def attention_lib(head_dim: int):
     lib = _attn_libs.get(head_dim)
     if lib is None:
@@ -797,7 +840,7 @@ def attention_oproj(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 # Activations of the gated epilogue, by the code that the kernels take as their ``gated`` argument
 # (0 means "no gate").  The gate is applied in float32 inside the product's epilogue; an activation
 # that is not built is refused here by name, before anything is launched.
-GATED_ACTIVATIONS = {"silu": 1}
+GATED_ACTIVATIONS = {"silu": 1, "gelu_tanh": 2}
 
 
 def gated_activation_code(activation: str) -> int:
@@ -828,5 +871,117 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, activation: str = "si
         return out
     gu = torch.empty((M, 2 * I), dtype=x.dtype, device=x.device)
     gemm_simt(x, w_gate_up, None, gu)
-    silu_mul(gu, out)
+    silu_mul(gu, out, code)
     return out
+
+
+# ------------------------------------------------------------------------------------
+# Mixers with a state of fixed size per request (csrc/recurrent.cu, a library of its own that is
+# compiled when a model with such a mixer is first run).
+def recurrent():
+    global _recurrent
+    if _recurrent is None:
+        lib = build.recurrent_library()
+        lib.coheryn_last_error.restype = ctypes.c_char_p
+        lib.coheryn_launch_count.restype = ctypes.c_ulonglong
+        _recurrent = lib
+    return _recurrent
+
+
+def _f32(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.float32 or t.stride(-1) != 1:
+        raise KernelError(f"{name} must be float32 with contiguous rows")
+
+
+def short_conv_silu(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, step, update_state: bool = True) -> torch.Tensor:
+    """y[t, c] = silu(sum_j taps[c, j] * x[t - (n-1) + j, c]) over each request's run of tokens; inputs before the
+    step's first token come from ``state`` (a float32 view [slots, (n-1) * C] whose rows may be strided), which then
+    receives the last n-1 inputs.  ``x`` float32 [T, C] (a column slice is fine); returns float32 [T, C]."""
+    _dev(x, taps, state, step.token_req, step.cu_q, step.state_slots)
+    _f32(x, "x"); _f32(state, "state")
+    T, C = x.shape
+    n = taps.shape[1]
+    assert taps.shape == (C, n) and taps.is_contiguous() and state.shape[1] == (n - 1) * C
+    y = torch.empty((T, C), dtype=torch.float32, device=x.device)
+    lib = recurrent()
+    _check(lib, lib.coheryn_short_conv_silu(
+        _ptr(x), c_long(x.stride(0)), _ptr(y), c_long(y.stride(0)), _ptr(taps), c_int(_code(taps)), c_int(n), c_int(C),
+        _ptr(state), c_long(state.stride(0)), _ptr(step.token_req), _ptr(step.cu_q), _ptr(step.state_slots), c_int(T),
+        c_int(step.num_requests), c_int(1 if update_state else 0), _stream()))
+    return y
+
+
+def gated_delta_scan(q, k, v, beta, step_pre, step_bias, rate_log, state, step, heads: int, kv_heads: int, dk: int, dv: int,
+                     out: torch.Tensor, norm_weight: torch.Tensor, gate: torch.Tensor, eps: float, out_scale: float = 1.0) -> None:
+    """The gated delta rule over each request's run of tokens, continued from and left in ``state`` (float32 view
+    [slots, heads * dk * dv]), followed by the per-head RMS norm, its weight ([dv], shared by the heads) and the sigmoid of
+    ``gate``.  q, k [T, kv_heads*dk] and v [T, heads*dv]: float32 with ONE row stride (slices of one buffer); beta [T, heads],
+    step_pre [T, heads*dk], gate [T, heads*dv]: float32 pre-activations; out [T, heads*dv] in the compute dtype."""
+    _dev(q, k, v, beta, step_pre, step_bias, rate_log, state, out, norm_weight, gate)
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (beta, "beta"), (step_pre, "step"), (state, "state"), (gate, "gate")):
+        _f32(t, name)
+    assert q.stride(0) == k.stride(0) == v.stride(0)
+    assert q.shape[1] == kv_heads * dk and k.shape[1] == kv_heads * dk and v.shape[1] == heads * dv
+    assert beta.shape[1] == heads and step_pre.shape[1] == heads * dk and gate.shape[1] == heads * dv
+    assert step_bias.numel() == heads * dk and rate_log.numel() == heads and norm_weight.numel() == dv
+    assert state.shape[1] == heads * dk * dv and out.shape == (q.shape[0], heads * dv) and out.stride(1) == 1
+    lib = recurrent()
+    _check(lib, lib.coheryn_gated_delta_scan(
+        _ptr(q), _ptr(k), _ptr(v), c_long(q.stride(0)), _ptr(beta), c_long(beta.stride(0)), _ptr(step_pre),
+        c_long(step_pre.stride(0)), _ptr(step_bias), c_int(_code(step_bias)), _ptr(rate_log), c_int(_code(rate_log)),
+        _ptr(state), c_long(state.stride(0)), _ptr(step.cu_q), _ptr(step.state_slots), c_int(step.num_requests),
+        c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv), _ptr(out), c_int(_code(out)), c_long(out.stride(0)),
+        _ptr(norm_weight), c_int(_code(norm_weight)), c_int(0), _ptr(gate), c_long(gate.stride(0)), c_float(eps),
+        c_float(out_scale), _stream()))
+
+
+def matrix_memory_scan(q, k, v, gate_i, gate_f, bias_i, bias_f, cap: float, state, step, heads: int, dk: int, dv: int,
+                       out: torch.Tensor, norm_weight: torch.Tensor, gate: torch.Tensor, eps: float, out_scale: float = 1.0) -> None:
+    """The stabilised matrix memory over each request's run of tokens, continued from and left in ``state`` (float32
+    view [slots, heads * (dk * dv + dk + 1)]: S, n, m), followed by the per-head RMS norm, its weight [heads*dv] and the
+    sigmoid of ``gate``.  q, k [T, heads*dk], v [T, heads*dv]: float32 with one row stride; gate_i, gate_f [T, heads] with
+    one row stride; biases [heads]; out [T, heads*dv] in the compute dtype."""
+    _dev(q, k, v, gate_i, gate_f, bias_i, bias_f, state, out, norm_weight, gate)
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (gate_i, "gate_i"), (gate_f, "gate_f"), (state, "state"), (gate, "gate")):
+        _f32(t, name)
+    assert q.stride(0) == k.stride(0) == v.stride(0) and gate_i.stride(0) == gate_f.stride(0)
+    assert q.shape[1] == heads * dk and k.shape[1] == heads * dk and v.shape[1] == heads * dv
+    assert gate_i.shape[1] == heads and gate_f.shape[1] == heads and gate.shape[1] == heads * dv
+    assert bias_i.numel() == heads and bias_f.numel() == heads and bias_i.dtype == bias_f.dtype
+    assert norm_weight.numel() == heads * dv
+    assert state.shape[1] == heads * (dk * dv + dk + 1) and out.shape == (q.shape[0], heads * dv) and out.stride(1) == 1
+    lib = recurrent()
+    _check(lib, lib.coheryn_matrix_memory_scan(
+        _ptr(q), _ptr(k), _ptr(v), c_long(q.stride(0)), _ptr(gate_i), _ptr(gate_f), c_long(gate_i.stride(0)), _ptr(bias_i),
+        _ptr(bias_f), c_int(_code(bias_i)), c_float(cap), _ptr(state), c_long(state.stride(0)), _ptr(step.cu_q),
+        _ptr(step.state_slots), c_int(step.num_requests), c_int(heads), c_int(dk), c_int(dv), _ptr(out), c_int(_code(out)),
+        c_long(out.stride(0)), _ptr(norm_weight), c_int(_code(norm_weight)), c_int(dv), _ptr(gate), c_long(gate.stride(0)),
+        c_float(eps), c_float(out_scale), _stream()))
+
+
+def qk_norm_kv_write(q, k, v, q_weight, k_weight, eps: float, slots, k_cache, v_cache, num_heads: int, num_kv_heads: int,
+                     dk: int, dv: int, page_size: int, dtype: torch.dtype) -> torch.Tensor:
+    """Queries and keys divided by the root mean square of their WHOLE projection (all heads at once) and multiplied by
+    a weight (skipped when ``q_weight`` is None); keys and values written into cache pages ``[page, kv head, slot, size]``
+    at ``slots`` (None: nothing is written).  q, k, v: float32 with one row stride.  Returns q [T, heads*dk] in ``dtype``."""
+    _dev(q, k, v, q_weight, k_weight, slots, k_cache, v_cache)
+    for t, name in ((q, "q"), (k, "k"), (v, "v")):
+        _f32(t, name)
+    assert q.stride(0) == k.stride(0) == v.stride(0)
+    T = q.shape[0]
+    assert q.shape[1] == num_heads * dk and k.shape[1] == num_kv_heads * dk and v.shape[1] == num_kv_heads * dv
+    normalise = q_weight is not None
+    if normalise:
+        assert q_weight.numel() == num_heads * dk and k_weight.numel() == num_kv_heads * dk and q_weight.dtype == k_weight.dtype
+    if slots is not None:
+        _i32(slots, "slots")
+        assert k_cache.dtype == dtype and v_cache.dtype == dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, dk) and tuple(v_cache.shape[1:]) == (num_kv_heads, page_size, dv)
+    q_out = torch.empty((T, num_heads * dk), dtype=dtype, device=q.device)
+    lib = recurrent()
+    _check(lib, lib.coheryn_qk_norm_kv_write(
+        _ptr(q), _ptr(k), _ptr(v), c_long(q.stride(0)), _ptr(q_weight), _ptr(k_weight),
+        c_int(_code(q_weight) if normalise else F32), c_float(eps), c_int(1 if normalise else 0), _ptr(q_out),
+        c_int(_CODES[dtype]), c_long(q_out.stride(0)), _ptr(slots), _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(num_heads),
+        c_int(num_kv_heads), c_int(dk), c_int(dv), c_int(page_size), _stream()))
+    return q_out

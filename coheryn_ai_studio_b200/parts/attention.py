@@ -132,4 +132,80 @@ class Attention(Mixer):
         return ops.linear(o, self.w_o, self.b_o, partial_ok=self.partial_output)
 
 
+class DistanceBiasAttention(Mixer):
+    """Grouped-query causal attention without rotation: the score of key j for query i is
+    (q . k) * scale - slope_h * (i - j), slope_h = 2^(-slope_exponent (h + 1) / heads) for head h (None: no bias);
+    a ``window`` keeps the keys with i - j < window; ordinary softmax.  ``qk_norm = "projection"`` divides the
+    WHOLE query projection (all heads at once), and the whole key projection, by its root mean square and
+    multiplies by a weight (``q.norm``, ``k.norm``) before the heads are split.  Values may have another head
+    size than keys.  The output is multiplied by ``out_scale`` before the output projection."""
+
+    output_parts = 1
+
+    def __init__(self, runtime: Runtime, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 window: Optional[int], scale: float, v_head_dim: Optional[int] = None,
+                 slope_exponent: Optional[float] = 8.0, qk_norm: Optional[str] = None, eps: float = 1e-6,
+                 out_scale: float = 1.0):
+        super().__init__(runtime)
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} heads do not divide into {num_kv_heads} kv heads")
+        if window is not None and window < 1:
+            raise ValueError("an attention window must hold at least one position")
+        if qk_norm not in (None, "projection"):
+            raise ValueError(f"qk_norm {qk_norm!r} is not built (None, 'projection')")
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.dk, self.dv = int(head_dim), int(v_head_dim if v_head_dim is not None else head_dim)
+        self.window, self.scale, self.eps, self.out_scale = window, float(scale), float(eps), float(out_scale)
+        self.slope_exponent, self.qk_norm = slope_exponent, qk_norm
+        self.slopes = self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+
+    def cache_requirement(self):
+        return PagedKV(self.num_kv_heads, self.dk, self.window, None if self.dv == self.dk else self.dv)
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        W, H, G, dk, dv = self.hidden_size, self.num_heads, self.num_kv_heads, self.dk, self.dv
+        specs = {"q": TensorSpec((H * dk, W)), "k": TensorSpec((G * dk, W)), "v": TensorSpec((G * dv, W)),
+                 "o": TensorSpec((W, H * dv))}
+        if self.qk_norm is not None:
+            specs["q.norm"] = TensorSpec((H * dk,), role="vector", init="norm")
+            specs["k.norm"] = TensorSpec((G * dk,), role="vector", init="norm")
+        return specs
+
+    def bind(self, tensors):
+        self.w_qkv = torch.cat([tensors["q"], tensors["k"], tensors["v"]], dim=0).contiguous()
+        self.w_o = tensors["o"]
+        if self.qk_norm is not None:
+            qn, kn = tensors["q.norm"], tensors["k.norm"]
+            dt = torch.float32 if torch.float32 in (qn.dtype, kn.dtype) else qn.dtype
+            self.q_norm, self.k_norm = qn.to(dt).contiguous(), kn.to(dt).contiguous()
+        if self.slope_exponent is not None:
+            H = self.num_heads
+            self.slopes = torch.tensor([2.0 ** (-float(self.slope_exponent) * (h + 1) / H) for h in range(H)],
+                                       dtype=torch.float64).to(torch.float32).to(self.w_o.device)
+
+    def forward_into(self, x: torch.Tensor, step: StepContext, cache: LayerCache, out: torch.Tensor) -> None:
+        Attention._check(cache)
+        H, G, dk, dv = self.num_heads, self.num_kv_heads, self.dk, self.dv
+        nq, nk = H * dk, G * dk
+        if cache.writes:
+            proj = ops.linear(x, self.w_qkv, out_dtype=torch.float32)
+            slots = step.slots[cache.group]
+        else:       # keys and values another execution wrote: only the queries are made
+            proj = torch.empty((x.shape[0], self.w_qkv.shape[0]), dtype=torch.float32, device=x.device)
+            ops.linear(x, self.w_qkv[:nq], out=proj[:, :nq])
+            slots = None
+        q = ops.qk_norm_kv_write(proj[:, :nq], proj[:, nq:nq + nk], proj[:, nq + nk:], self.q_norm, self.k_norm, self.eps,
+                                 slots, cache.k, cache.v, H, G, dk, dv, cache.page_size, self.runtime.dtype)
+        o = torch.empty((x.shape[0], H * dv), dtype=self.runtime.dtype, device=x.device)
+        ops.attention_biased(q, o, cache.k, cache.v, step, cache.group, H, G, dk, dv, cache.page_size, self.window,
+                             self.scale, self.slopes, self.out_scale)
+        ops.linear(o, self.w_o, out=out[0])
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+        out = torch.empty((1, x.shape[0], self.hidden_size), dtype=torch.float32, device=x.device)
+        self.forward_into(x, step, cache, out)
+        return out if self.partial_output else out[0]
+
+
 register_mixer("attention", Attention)
+register_mixer("attention_distance_bias", DistanceBiasAttention)

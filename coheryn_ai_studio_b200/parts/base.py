@@ -43,6 +43,7 @@ class PagedKV:
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None      # values of another head size than keys (None: the same)
 
 
 @dataclass(frozen=True)
@@ -63,13 +64,15 @@ class LayerCache:
     Fixed state: ``state`` is ``[slots, *shape]``; ``step.state_slots`` gives each
     request's slot."""
 
-    kind: str                      # "paged" | "state"
+    kind: str                      # "paged" | "state" | "several"
     group: int = -1
     page_size: int = 0
     k: Optional[torch.Tensor] = None
     v: Optional[torch.Tensor] = None
     writes: bool = True
     state: Optional[torch.Tensor] = None
+    # "several": a mixer that asked for a tuple of requirements gets one cache per element, in order.
+    parts: Optional[List["LayerCache"]] = None
 
 
 @dataclass
@@ -141,7 +144,8 @@ class Mixer(Part):
         raise NotImplementedError
 
     def cache_requirement(self):
-        """PagedKV, FixedState or None."""
+        """PagedKV, FixedState, a tuple of those (a mixer made of several; its cache then has
+        ``parts``), or None."""
         return None
 
     def forward(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache]) -> torch.Tensor:
@@ -191,6 +195,7 @@ class Arrangement:
                              + (f"missing slots {missing} " if missing else "")
                              + f"(slots: {sorted(self.SLOTS)})")
         self.slots = dict(parts)
+        self.names: Optional[Dict[str, str]] = None     # LayerSpec.names, set by the model
         for name in self.SLOTS:
             setattr(self, name, parts.get(name))
 

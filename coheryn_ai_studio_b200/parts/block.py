@@ -9,6 +9,8 @@ from __future__ import annotations
 
 from typing import Dict
 
+import torch
+
 from .. import ops
 from .base import Arrangement, Part, register_arrangement
 from .native_block import NativeBlock
@@ -53,4 +55,38 @@ class PreNormResidual(Arrangement):
         return kept, out
 
 
+class ParallelResidual(Arrangement):
+    """x += mixer(h) + feed_forward(h) with ONE norm h = norm(x) that both read; the feed-forward may be absent.
+    The summands are not added here: each part writes its own (a mixer made of several writes several) into a
+    float32 stack that the NEXT norm adds to the stream in order while it normalises, so the block needs parts
+    that offer ``output_parts`` and ``forward_into`` and a model whose norms all take partial sums."""
+
+    SLOTS = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
+    OPTIONAL = ("feed_forward",)
+    NAMES = {"norm": "input_layernorm", "mixer": "mixer", "feed_forward": "mlp"}
+
+    def __init__(self, parts):
+        super().__init__(parts)
+        for part in self.producers():
+            if not hasattr(part, "forward_into"):
+                raise ValueError(f"parallel_residual: {type(part).__name__} cannot write its output into a stack of summands")
+
+    def parts(self) -> Dict[str, Part]:
+        names = self.names or self.NAMES
+        return {names[slot]: part for slot, part in self.slots.items()}
+
+    def forward(self, residual, delta, step, cache):
+        if not self.mixer.partial_output:
+            raise ValueError("parallel_residual needs a model whose norms all take partial sums")
+        h = self.norm.forward(residual, delta)
+        n_mix = self.mixer.output_parts
+        n = n_mix + (self.feed_forward.output_parts if self.feed_forward is not None else 0)
+        out = torch.empty((n, residual.shape[0], residual.shape[1]), dtype=torch.float32, device=residual.device)
+        self.mixer.forward_into(h, step, cache, out[:n_mix])
+        if self.feed_forward is not None:
+            self.feed_forward.forward_into(h, step, out[n_mix:])
+        return residual, out
+
+
 register_arrangement("prenorm_residual", PreNormResidual)
+register_arrangement("parallel_residual", ParallelResidual)

@@ -1,5 +1,5 @@
-"""Dense gated feed-forward: y = W_down (act(W_gate x) * (W_up x)), no biases; here act = silu (SwiGLU),
-silu(g) = g / (1 + exp(-g)) in float32
+"""Dense gated feed-forward: y = W_down (act(W_gate x) * (W_up x)), no biases; act = silu (SwiGLU),
+silu(g) = g / (1 + exp(-g)), or the tanh form of GELU, in float32
 (crates/coheryn-engine/src/inference.rs:516-540, crates/coheryn-engine/src/cpu.rs:74-78).
 """
 from __future__ import annotations
@@ -14,8 +14,11 @@ from .base import FeedForward, Runtime, StepContext, register_feed_forward
 
 
 class GatedMLP(FeedForward):
-    def __init__(self, runtime: Runtime, hidden_size: int, intermediate_size: int, activation: str):
+    def __init__(self, runtime: Runtime, hidden_size: int, intermediate_size: int, activation: str,
+                 tensors=("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
+        """``tensors``: the local names of the gate, up and down matrices in the checkpoint."""
         super().__init__(runtime)
+        self.names = tuple(tensors)
         ops.gated_activation_code(activation)     # refuses, by name, an activation the epilogues lack
         self.activation = activation
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
@@ -23,19 +26,25 @@ class GatedMLP(FeedForward):
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         H, I = self.hidden_size, self.intermediate_size
-        return {"gate_proj.weight": TensorSpec((I, H)), "up_proj.weight": TensorSpec((I, H)),
-                "down_proj.weight": TensorSpec((H, I))}
+        g, u, d = self.names
+        return {g: TensorSpec((I, H)), u: TensorSpec((I, H)), d: TensorSpec((H, I))}
 
     def bind(self, tensors):
         # One matrix product for gate and up, rows interleaved (2j = gate_j, 2j+1 = up_j) so
         # that the gated epilogue finds a pair in neighbouring output columns.
-        g, u = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        g, u = tensors[self.names[0]], tensors[self.names[1]]
         self.w_gate_up = torch.stack([g, u], dim=1).reshape(2 * g.shape[0], g.shape[1]).contiguous()
-        self.w_down = tensors["down_proj.weight"]
+        self.w_down = tensors[self.names[2]]
 
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
         act = ops.gated_linear(x, self.w_gate_up, self.activation)
         return ops.linear(act, self.w_down, partial_ok=self.partial_output)
+
+    output_parts = 1
+
+    def forward_into(self, x: torch.Tensor, step: StepContext, out: torch.Tensor) -> None:
+        """The output written into ``out`` (float32 [1, T, H]): one of the summands that a block hands to the next norm."""
+        ops.linear(ops.gated_linear(x, self.w_gate_up, self.activation), self.w_down, out=out[0])
 
 
 register_feed_forward("gated_mlp", GatedMLP)

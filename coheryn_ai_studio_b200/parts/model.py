@@ -11,7 +11,7 @@ import torch
 from .. import ops
 from ..config.spec import ModelSpec
 from ..weights.spec import TensorSpec
-from . import attention, block, feedforward, norm, position  # noqa: F401  (register the stock parts)
+from . import attention, block, feedforward, norm, position, recurrent  # noqa: F401  (register the stock parts)
 from .base import (ARRANGEMENTS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, LayerCache, Part,
                    Runtime, StepContext, build_part)
 
@@ -42,7 +42,9 @@ class DecoderModel:
                                      f"(slots: {sorted(arr.SLOTS)})")
                 extra = {"position": pos} if role == "mixer" and pos is not None else {}
                 built[slot] = build_part(tables[role], role, part_spec, runtime, **extra)
-            self.layers.append(arr(built))
+            layer = arr(built)
+            layer.names = dict(ls.names) if ls.names is not None else None
+            self.layers.append(layer)
         self.final_norm = build_part(NORMS, "norm", spec.final_norm, runtime)
         # Outputs go from a layer to the NEXT norm (the following layer's, or the final one),
         # so partial sums may flow only if every norm of the model can add them.
@@ -56,6 +58,7 @@ class DecoderModel:
         self.embedding: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
         self.head_bias: Optional[torch.Tensor] = None
+        self.extra: Dict[str, torch.Tensor] = {}
         self.status = None
         # Called with (schedule entry, float32 [T, H] output of that entry) when set: the layer
         # outputs of a trace (crates/coheryn-engine/src/inference.rs:541-543).  Off in serving.
@@ -70,28 +73,38 @@ class DecoderModel:
         out.append((self.spec.final_norm_name, self.final_norm))
         return out
 
+    @staticmethod
+    def _join(prefix: str, local: str) -> str:
+        return f"{prefix}.{local}" if local else prefix       # a part may name its one tensor as the part is named
+
+    def _matrix_name(self, name: str) -> str:
+        return name if self.spec.bare_tensor_names else f"{name}.weight"
+
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         """Every tensor the checkpoint must hold, by its full name."""
         s = self.spec
-        specs = {f"{s.embedding_name}.weight": TensorSpec((s.vocab_size, s.hidden_size))}
+        specs = {self._matrix_name(s.embedding_name): TensorSpec((s.vocab_size, s.hidden_size))}
         for prefix, part in self._named_parts():
             for local, ts in part.tensor_specs().items():
-                specs[f"{prefix}.{local}"] = ts
+                specs[self._join(prefix, local)] = ts
         if s.head_name is not None:
-            specs[f"{s.head_name}.weight"] = TensorSpec((s.vocab_size, s.hidden_size))
+            specs[self._matrix_name(s.head_name)] = TensorSpec((s.vocab_size, s.hidden_size))
         if s.head_bias_name is not None:
             specs[s.head_bias_name] = TensorSpec((s.vocab_size,), role="vector", init="bias")
+        for name, (shape, role, init) in s.extra_tensors.items():
+            specs[name] = TensorSpec(tuple(shape), role=role, init=init)
         return specs
 
     def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
         s = self.spec
-        self.embedding = tensors[f"{s.embedding_name}.weight"]
+        self.embedding = tensors[self._matrix_name(s.embedding_name)]
         for prefix, part in self._named_parts():
-            local = {name: tensors[f"{prefix}.{name}"] for name in part.tensor_specs()
-                     if f"{prefix}.{name}" in tensors}
+            local = {name: tensors[self._join(prefix, name)] for name in part.tensor_specs()
+                     if self._join(prefix, name) in tensors}
             part.bind(local)
-        self.head = tensors[f"{s.head_name}.weight"] if s.head_name is not None else self.embedding
+        self.head = tensors[self._matrix_name(s.head_name)] if s.head_name is not None else self.embedding
         self.head_bias = tensors[s.head_bias_name] if s.head_bias_name is not None else None
+        self.extra = {name: tensors[name] for name in s.extra_tensors}
         self.status = torch.zeros(1, dtype=torch.int32, device=self.runtime.device)
 
     # ------------------------------------------------------------------ cache needs
@@ -117,6 +130,11 @@ class DecoderModel:
         tailed = False
         for i, (entry, cache) in enumerate(zip(self.spec.schedule, caches)):
             layer = self.layers[entry.layer]
+            if entry.inject is not None:
+                # added to the stream itself; what the previous entry handed on stays pending beside it
+                vec = entry.inject.vector
+                ops.stream_inject(residual, self.embedding if entry.inject.embedding else None, step.token_ids,
+                                  self.spec.embedding_scale, self.extra[vec[0]][vec[1]] if vec is not None else None)
             if i == last and step.tail is not None and layer.supports_tail and self.layer_observer is None:
                 residual, delta = layer.forward_tail(residual, delta, step, cache)
                 tailed = True
@@ -130,6 +148,6 @@ class DecoderModel:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.runtime.device)
         h = self.final_norm.forward(residual, delta, rows=None if tailed else logit_rows)
         logits = ops.linear(h, self.head, out_dtype=torch.float32)
-        if self.spec.logit_scale is not None or self.head_bias is not None:
-            ops.scale_add_bias(logits, self.spec.logit_scale, self.head_bias)
+        if self.spec.logit_scale is not None or self.head_bias is not None or self.spec.logit_softcap is not None:
+            ops.scale_add_bias(logits, self.spec.logit_scale, self.head_bias, self.spec.logit_softcap)
         return logits

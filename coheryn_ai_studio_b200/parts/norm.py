@@ -18,16 +18,17 @@ from .base import Norm, Runtime, register_norm
 class RMSNorm(Norm):
     accepts_partial_sums = True
 
-    def __init__(self, runtime: Runtime, size: int, eps: float):
+    def __init__(self, runtime: Runtime, size: int, eps: float, tensor: str = "weight"):
+        """``tensor``: the local name of the weight ("" when the checkpoint names the weight as it names the norm)."""
         super().__init__(runtime)
-        self.size, self.eps = int(size), float(eps)
+        self.size, self.eps, self.tensor = int(size), float(eps), str(tensor)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.size,), role="vector", init="norm")}
+        return {self.tensor: TensorSpec((self.size,), role="vector", init="norm")}
 
     def bind(self, tensors):
-        self.weight = tensors["weight"]
+        self.weight = tensors[self.tensor]
 
     def forward(self, residual, delta, rows=None):
         """residual += delta (when given and no ``rows``); returns the normalised rows in

@@ -1,0 +1,210 @@
+"""Mixers that keep a state of fixed size per request instead of keys and values per position, and the mixer
+that runs several mixers side by side.
+
+* ``MatrixMemory`` (kind ``matrix_memory``): the stabilised matrix memory of xLSTM (mLSTM).  Per head, with
+  q = W_q h / sqrt(d), k = W_k h, v = W_v h and the capped log gates i = c tanh((W_i h + b_i) / c),
+  f = log sigmoid(c tanh((W_f h + b_f) / c)):  m' = max(f + m, i);  S' = e^(f + m - m') S + e^(i - m') k v^T;
+  n' likewise with k alone;  o = S'^T q / (max(|n' . q|, e^(-m')) + 1e-6).  m starts at 0.  Each head's o is
+  divided by its root mean square, the heads are multiplied by a weight and by sigmoid(W_g h), then W_o.
+* ``GatedDeltaRule`` (kind ``gated_delta_rule``): q, k (kv heads) and v (heads) pass a short causal convolution
+  per channel and SiLU; q and k become unit vectors per head (q also / sqrt(d)); beta = sigmoid(W_b h); one decay
+  per head and key channel g = exp(-exp(A_log) softplus(W_a2 W_a1 h + dt_bias));  S <- diag(g) S;
+  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.  Each head's o is divided by its root mean square,
+  multiplied by a weight shared by the heads and by sigmoid(W_g2 W_g1 h), then W_o.  The last taps-1 inputs
+  of the convolutions are part of the state.
+* ``SideBySide`` (kind ``side_by_side``): mixers that read the same input; the result is the weighted sum of
+  theirs.  Each child multiplies its own output by its weight before its output projection, and the
+  children's outputs go to the next norm as separate summands.
+
+Everything that enters a recurrence is float32: the projections are computed by the matrix products of the
+compute dtype with float32 accumulation and handed on as float32; gates, decays, unit norms, the state and the
+norm of the output are computed in float32 inside the scan kernels (``csrc/recurrent.cu``).  All projections
+that read the mixer's input are one matrix product over the stacked weights.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional, Sequence, Tuple
+
+import torch
+
+from .. import ops
+from ..config.spec import PartSpec
+from ..weights.spec import TensorSpec
+from .base import MIXERS, FixedState, LayerCache, Mixer, Runtime, StepContext, build_part, register_mixer
+
+
+class _StackedInput:
+    """Rows of several weight matrices stacked so that one product makes all projections of an input;
+    ``cut`` hands back the column range of each."""
+
+    def __init__(self, named: Sequence[Tuple[str, torch.Tensor]]):
+        self.weight = torch.cat([w for _, w in named], dim=0).contiguous()
+        self.ranges, at = {}, 0
+        for name, w in named:
+            self.ranges[name] = (at, at + w.shape[0])
+            at += w.shape[0]
+
+    def project(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.linear(x, self.weight, out_dtype=torch.float32)
+
+    def cut(self, proj: torch.Tensor, first: str, last: Optional[str] = None) -> torch.Tensor:
+        return proj[:, self.ranges[first][0]:self.ranges[last or first][1]]
+
+
+class _StateMixer(Mixer):
+    output_parts = 1
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache]) -> torch.Tensor:
+        out = torch.empty((1, x.shape[0], self.hidden_size), dtype=torch.float32, device=x.device)
+        self.forward_into(x, step, cache, out)
+        return out if self.partial_output else out[0]
+
+    @staticmethod
+    def _state_of(cache: Optional[LayerCache]) -> torch.Tensor:
+        if cache is None or cache.kind != "state":
+            raise ValueError("this mixer needs a state slot per request")
+        if not cache.writes:
+            raise ValueError("a recurrent state cannot be shared between two executions of a layer")
+        return cache.state
+
+
+class MatrixMemory(_StateMixer):
+    def __init__(self, runtime: Runtime, hidden_size: int, num_heads: int, head_dim: int, v_head_dim: int,
+                 gate_cap: float, eps: float, out_scale: float = 1.0):
+        super().__init__(runtime)
+        self.hidden_size, self.num_heads = int(hidden_size), int(num_heads)
+        self.dk, self.dv, self.cap, self.eps, self.out_scale = int(head_dim), int(v_head_dim), float(gate_cap), float(eps), float(out_scale)
+        if not self.cap > 0:
+            raise ValueError("the gate cap must be positive")
+        self.stacked = self.w_o = self.norm_w = self.b_i = self.b_f = None
+
+    def cache_requirement(self):
+        H, dk, dv = self.num_heads, self.dk, self.dv
+        return FixedState((H * (dk * dv + dk + 1),), torch.float32)     # S, n, m of every head
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        W, H, dk, dv = self.hidden_size, self.num_heads, self.dk, self.dv
+        return {"q": TensorSpec((H * dk, W)), "k": TensorSpec((H * dk, W)), "v": TensorSpec((H * dv, W)),
+                "g": TensorSpec((H * dv, W)), "o": TensorSpec((W, H * dv)),
+                "norm": TensorSpec((H * dv,), role="vector", init="norm"),
+                "i": TensorSpec((H, W)), "i.b": TensorSpec((H,), role="vector", init="bias"),
+                "f": TensorSpec((H, W)), "f.b": TensorSpec((H,), role="vector", init="bias")}
+
+    def bind(self, tensors):
+        self.stacked = _StackedInput([(n, tensors[n]) for n in ("q", "k", "v", "g", "i", "f")])
+        self.w_o, self.norm_w = tensors["o"], tensors["norm"]
+        dt = torch.float32 if torch.float32 in (tensors["i.b"].dtype, tensors["f.b"].dtype) else tensors["i.b"].dtype
+        self.b_i, self.b_f = tensors["i.b"].to(dt).contiguous(), tensors["f.b"].to(dt).contiguous()
+
+    def forward_into(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], out: torch.Tensor) -> None:
+        state = self._state_of(cache)
+        st, proj = self.stacked, self.stacked.project(x)
+        o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
+        ops.matrix_memory_scan(st.cut(proj, "q"), st.cut(proj, "k"), st.cut(proj, "v"), st.cut(proj, "i"), st.cut(proj, "f"),
+                               self.b_i, self.b_f, self.cap, state, step, self.num_heads, self.dk, self.dv, o, self.norm_w,
+                               st.cut(proj, "g"), self.eps, self.out_scale)
+        ops.linear(o, self.w_o, out=out[0])
+
+
+class GatedDeltaRule(_StateMixer):
+    def __init__(self, runtime: Runtime, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 v_head_dim: int, conv_taps: int, eps: float, decay_rank: Optional[int] = None,
+                 gate_rank: Optional[int] = None, out_scale: float = 1.0):
+        """``decay_rank`` / ``gate_rank``: the inner sizes of the two-step projections of the decay and of the output
+        gate; None takes them from the checkpoint's tensors."""
+        super().__init__(runtime)
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} heads do not divide into {num_kv_heads} query/key heads")
+        if not 1 <= conv_taps <= 16:
+            raise ValueError("the short convolution takes 1 to 16 taps")
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.dk, self.dv, self.taps, self.eps, self.out_scale = int(head_dim), int(v_head_dim), int(conv_taps), float(eps), float(out_scale)
+        self.decay_rank, self.gate_rank = decay_rank, gate_rank
+        self.channels = 2 * self.num_kv_heads * self.dk + self.num_heads * self.dv
+        self.memory = self.num_heads * self.dk * self.dv
+
+    def cache_requirement(self):
+        return FixedState((self.memory + (self.taps - 1) * self.channels,), torch.float32)   # S of every head, then the convolutions' inputs
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        W, H, G, dk, dv, n = self.hidden_size, self.num_heads, self.num_kv_heads, self.dk, self.dv, self.taps
+        ra, rg = self.decay_rank or -1, self.gate_rank or -1      # -1: any size, as the checkpoint has it
+        return {"q": TensorSpec((G * dk, W)), "q.conv": TensorSpec((G * dk, n), role="vector", init="conv"),
+                "k": TensorSpec((G * dk, W)), "k.conv": TensorSpec((G * dk, n), role="vector", init="conv"),
+                "v": TensorSpec((H * dv, W)), "v.conv": TensorSpec((H * dv, n), role="vector", init="conv"),
+                "b": TensorSpec((H, W)), "A_log": TensorSpec((H,), role="vector", init="bias"),
+                "norm": TensorSpec((dv,), role="vector", init="norm"),
+                "a1": TensorSpec((ra, W)), "a2": TensorSpec((H * dk, ra)),
+                "dt_bias": TensorSpec((H * dk,), role="vector", init="bias"),
+                "g1": TensorSpec((rg, W)), "g2": TensorSpec((H * dv, rg)), "o": TensorSpec((W, H * dv))}
+
+    def bind(self, tensors):
+        if tensors["a1"].shape[0] != tensors["a2"].shape[1] or tensors["g1"].shape[0] != tensors["g2"].shape[1]:
+            raise ValueError("the two steps of a low-rank projection do not fit each other")
+        self.stacked = _StackedInput([(n, tensors[n]) for n in ("q", "k", "v", "b", "a1", "g1")])
+        convs = [tensors["q.conv"], tensors["k.conv"], tensors["v.conv"]]
+        dt = torch.float32 if any(c.dtype == torch.float32 for c in convs) else convs[0].dtype
+        self.conv_w = torch.cat([c.to(dt) for c in convs], dim=0).contiguous()
+        self.w_a2, self.w_g2, self.w_o = tensors["a2"], tensors["g2"], tensors["o"]
+        self.rate_log, self.dt_bias, self.norm_w = tensors["A_log"], tensors["dt_bias"], tensors["norm"]
+
+    def forward_into(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], out: torch.Tensor) -> None:
+        state = self._state_of(cache)
+        st, proj = self.stacked, self.stacked.project(x)
+        G, H, dk, dv = self.num_kv_heads, self.num_heads, self.dk, self.dv
+        qkv = ops.short_conv_silu(st.cut(proj, "q", "v"), self.conv_w, state[:, self.memory:], step)
+        step_pre = ops.linear(st.cut(proj, "a1"), self.w_a2, out_dtype=torch.float32)
+        gate = ops.linear(st.cut(proj, "g1"), self.w_g2, out_dtype=torch.float32)
+        o = torch.empty((x.shape[0], H * dv), dtype=self.runtime.dtype, device=x.device)
+        ops.gated_delta_scan(qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], st.cut(proj, "b"), step_pre,
+                             self.dt_bias, self.rate_log, state[:, :self.memory], step, H, G, dk, dv, o, self.norm_w, gate,
+                             self.eps, self.out_scale)
+        ops.linear(o, self.w_o, out=out[0])
+
+
+class SideBySide(Mixer):
+    def __init__(self, runtime: Runtime, hidden_size: int, mixers: Sequence[Tuple[str, PartSpec, float]], position=None):
+        """``mixers``: (name under which the child's tensors stand, the child's PartSpec, the weight of its output)."""
+        super().__init__(runtime)
+        self.hidden_size = int(hidden_size)
+        if not mixers:
+            raise ValueError("side_by_side needs at least one mixer")
+        self.children = []
+        for name, spec, weight in mixers:
+            extra = {"position": position} if position is not None else {}
+            child = build_part(MIXERS, "mixer", spec, runtime, out_scale=float(weight), **extra)
+            if not hasattr(child, "forward_into"):
+                raise ValueError(f"side_by_side: {type(child).__name__} cannot write its output into a stack of summands")
+            self.children.append((str(name), child))
+        self.output_parts = sum(c.output_parts for _, c in self.children)
+        self.capturable = all(c.capturable for _, c in self.children)
+
+    def cache_requirement(self):
+        return tuple(c.cache_requirement() for _, c in self.children)
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        return {f"{name}.{local}": ts for name, c in self.children for local, ts in c.tensor_specs().items()}
+
+    def bind(self, tensors):
+        for name, c in self.children:
+            c.bind({local: tensors[f"{name}.{local}"] for local in c.tensor_specs() if f"{name}.{local}" in tensors})
+
+    def forward_into(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], out: torch.Tensor) -> None:
+        if cache is None or cache.kind != "several" or len(cache.parts) != len(self.children):
+            raise ValueError("side_by_side needs one cache per child")
+        at = 0
+        for (_, c), sub in zip(self.children, cache.parts):
+            c.forward_into(x, step, sub, out[at:at + c.output_parts])
+            at += c.output_parts
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache]) -> torch.Tensor:
+        out = torch.empty((self.output_parts, x.shape[0], self.hidden_size), dtype=torch.float32, device=x.device)
+        self.forward_into(x, step, cache, out)
+        if self.partial_output:
+            return out
+        raise ValueError("side_by_side hands its children's outputs on as summands and needs norms that add them")
+
+
+register_mixer("matrix_memory", MatrixMemory)
+register_mixer("gated_delta_rule", GatedDeltaRule)
+register_mixer("side_by_side", SideBySide)

@@ -57,7 +57,8 @@ def check_against(expected: Dict[str, TensorSpec], entries) -> None:
         e = entries.get(n)
         if e is None:
             continue
-        if tuple(e.shape) != tuple(s.shape):
+        # a size of -1 in the wanted shape stands for "as the checkpoint has it"
+        if len(e.shape) != len(s.shape) or any(w != -1 and int(f) != int(w) for f, w in zip(e.shape, s.shape)):
             wrong_shape.append((n, tuple(e.shape), tuple(s.shape)))
         is_int = e.dtype == torch.int32
         if is_int != (s.role == "int_table"):
@@ -111,6 +112,7 @@ class InitPolicy:
     matrix_std: float = 0.02
     bias_std: float = 0.02
     norm_jitter: float = 0.01
+    conv_std: float = 0.5          # taps of short convolutions
 
 
 def random_tensors(expected: Dict[str, TensorSpec], seed: int, policy: InitPolicy,
@@ -134,9 +136,11 @@ def random_tensors(expected: Dict[str, TensorSpec], seed: int, policy: InitPolic
         if spec.init == "zeros":
             out[name] = torch.zeros(spec.shape, dtype=dt, device=device)
             continue
+        if any(d < 0 for d in spec.shape):
+            raise ValueError(f"tensor {name}: a size that only a checkpoint gives must be named to make random weights")
         try:
             mean, deviation = {"normal": (0.0, policy.matrix_std), "bias": (0.0, policy.bias_std),
-                               "norm": (1.0, policy.norm_jitter)}[spec.init]
+                               "norm": (1.0, policy.norm_jitter), "conv": (0.0, policy.conv_std)}[spec.init]
         except KeyError:
             raise ValueError(f"tensor {name}: unknown init {spec.init!r}") from None
         out[name] = seeded_tensor(seed, name, spec.shape, mean, deviation, dtype=dt, device=device)
