@@ -121,6 +121,9 @@ def _check_layer(L: Dict[str, Any], what: str) -> None:
         _num(left, "scale", what + ".mixer.left")
         _int(_obj(left.get("mask"), what + ".mixer.left.mask"), "size", what + ".mixer.left.mask")
         _int(right, "conv", what + ".mixer.right", 1, 16)
+        for key in ("a_rank", "g_rank"):      # the inner sizes of the two-step projections: a checkpoint's tensors give
+            if key in right:                  # them; a configuration names them only so that random weights can be made
+                _int(right, key, what + ".mixer.right")
         _num(m, "left_scale", what + ".mixer", positive=False)
         _num(m, "right_scale", what + ".mixer", positive=False)
     else:
@@ -144,7 +147,8 @@ def _mixer_spec(L: Dict[str, Any], width: int, eps: float) -> PartSpec:
         qk_norm="projection", eps=eps))
     delta = PartSpec("gated_delta_rule", dict(
         hidden_size=width, num_heads=right["heads"], num_kv_heads=right["kv_heads"], head_dim=right["dim"],
-        v_head_dim=right["vdim"], conv_taps=right["conv"], eps=eps))
+        v_head_dim=right["vdim"], conv_taps=right["conv"], eps=eps,
+        decay_rank=right.get("a_rank"), gate_rank=right.get("g_rank")))
     return PartSpec("side_by_side", dict(hidden_size=width, mixers=(("left", attention, float(m["left_scale"])),
                                                                     ("right", delta, float(m["right_scale"])))))
 

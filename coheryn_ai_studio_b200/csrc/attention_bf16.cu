@@ -152,10 +152,13 @@ __device__ __forceinline__ float ex2_approx(float x) {
 //   Ks/Vs: [TB][KVS] tiles; key0: position of the tile's row 0; lo/hi[mi][h]: first and last
 //   visible key of the thread's rows g (h = 0) and g + 8 (h = 1) of row tile mi.  MASK false
 //   promises that every key of the tile is visible to every row.
-template <int MT, int TB, bool QSMEM, bool MASK, int KVS = LDS>
+//   BIAS: the score of a key loses slope * (row's position - key's position); sl[mi][h] is the slope of the
+//   thread's row (times log2 e), the row's position is its last visible key hi[mi][h].
+template <int MT, int TB, bool QSMEM, bool MASK, int KVS = LDS, bool BIAS = false>
 __device__ __forceinline__ void attend_tile(const unsigned (*qf)[4], const bf16* Qs, const bf16* Ks, const bf16* Vs,
                                             float (&o)[MT][HD / 8][4], RowState (&st)[MT], int key0,
-                                            const int (&lo)[MT][2], const int (&hi)[MT][2], float scale_log2) {
+                                            const int (&lo)[MT][2], const int (&hi)[MT][2], float scale_log2,
+                                            const float (*sl)[2] = nullptr) {
   const int lane = threadIdx.x & 31;
   const int t = lane & 3;
   const int id = lane >> 3, r = lane & 7;
@@ -204,6 +207,10 @@ __device__ __forceinline__ void attend_tile(const unsigned (*qf)[4], const bf16*
       for (int j = 0; j < TB / 8; ++j)
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
+          if constexpr (BIAS) {      // from here on s holds the scaled, biased score in the log2 domain
+            const int key = key0 + j * 8 + 2 * t + i;
+            s[mi][j][2 * h + i] = fmaf(s[mi][j][2 * h + i], scale_log2, sl[mi][h] * (float)(key - hi[mi][h]));
+          }
           if (MASK) {
             const int key = key0 + j * 8 + 2 * t + i;
             if (key < lo[mi][h] || key > hi[mi][h]) s[mi][j][2 * h + i] = -INFINITY;
@@ -212,7 +219,7 @@ __device__ __forceinline__ void attend_tile(const unsigned (*qf)[4], const bf16*
         }
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-      const float m_new = fmaxf(st[mi].m[h], mx * scale_log2);   // scale > 0 keeps the order
+      const float m_new = fmaxf(st[mi].m[h], BIAS ? mx : mx * scale_log2);   // scale > 0 keeps the order
       // Everything masked so far: keep the state and let every p be zero.
       const float m_use = m_new == -INFINITY ? 0.f : m_new;
       const float c = ex2_approx(st[mi].m[h] - m_use);
@@ -221,7 +228,7 @@ __device__ __forceinline__ void attend_tile(const unsigned (*qf)[4], const bf16*
       for (int j = 0; j < TB / 8; ++j)
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-          const float p = ex2_approx(fmaf(s[mi][j][2 * h + i], scale_log2, -m_use));
+          const float p = BIAS ? ex2_approx(s[mi][j][2 * h + i] - m_use) : ex2_approx(fmaf(s[mi][j][2 * h + i], scale_log2, -m_use));
           s[mi][j][2 * h + i] = p;
           part += p;
         }
@@ -300,7 +307,7 @@ attn_tiles_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ 
                   const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                   const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
                   const int* __restrict__ kv_lens, int nh, int nkv, int page_size, int window,
-                  float scale_log2, int skip_small) {
+                  float scale_log2, int skip_small, const float* __restrict__ slopes_log2) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* Qs = reinterpret_cast<bf16*>(smem_raw);                 // [BM][LDS]
   bf16* stages = Qs + BM * LDS;                                 // [2][K: TILE rows, V: TILE rows][LDS]
@@ -355,6 +362,7 @@ attn_tiles_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ 
 
   // Visible key range of the thread's rows, and of the warp's rows as a whole.
   int lo[1][2], hi[1][2];
+  float sl[1][2];
   const int w_row_first = row_first + rw * 16;
   const int w_row_last = min(rows - 1, w_row_first + 15);
   const bool w_active = w_row_first < rows;
@@ -367,6 +375,7 @@ attn_tiles_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ 
     } else {
       hi[0][h] = -1; lo[0][h] = 0;
     }
+    sl[0][h] = slopes_log2 ? slopes_log2[kvh * G + r % G] : 0.f;
   }
   const int w_hi_max = w_active ? base_pos + w_row_last / G : -1;           // last key any row sees
   const int w_hi_min = w_active ? base_pos + w_row_first / G : -1;          // last key EVERY row sees
@@ -393,7 +402,12 @@ attn_tiles_kernel(const bf16* __restrict__ q, long q_stride, bf16* __restrict__ 
     const int key0 = tile * TILE + kg * TBN;
     if (w_active && key0 <= w_hi_max && key0 + TBN > w_lo_min) {
       const bool all_visible = w_full && key0 + TBN - 1 <= w_hi_min && key0 >= w_lo_max;
-      if (all_visible)
+      if (slopes_log2) {
+        if (all_visible)
+          attend_tile<1, TBN, true, false, LDS, true>(nullptr, Qw, st_k, st_k + TILE * LDS, o, st, key0, lo, hi, scale_log2, sl);
+        else
+          attend_tile<1, TBN, true, true, LDS, true>(nullptr, Qw, st_k, st_k + TILE * LDS, o, st, key0, lo, hi, scale_log2, sl);
+      } else if (all_visible)
         attend_tile<1, TBN, true, false>(nullptr, Qw, st_k, st_k + TILE * LDS, o, st, key0, lo, hi, scale_log2);
       else
         attend_tile<1, TBN, true, true>(nullptr, Qw, st_k, st_k + TILE * LDS, o, st, key0, lo, hi, scale_log2);
@@ -503,7 +517,7 @@ attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict_
                    const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                    const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ cu_q,
                    const int* __restrict__ kv_lens, int nh, int nkv, int page_size, int window, float scale_log2,
-                   int split, int settled) {
+                   int split, int settled, const float* __restrict__ slopes_log2) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   __shared__ long long rowoff[SSTAGES][STILE];   // element offset of a tile's rows in a cache tensor, -1: not read
   __shared__ int pages_s[SPLIT_PAGES];           // block-table entries of the split's pages
@@ -587,6 +601,7 @@ attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict_
     ldmatrix_x4(qf[kd], Qs + (((lane >> 3) & 1) * 8 + (lane & 7)) * LDS + kd * 16 + (lane >> 4) * 8);
 
   int lo[1][2], hi[1][2];
+  float sl[1][2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = h * 8 + g;
@@ -596,6 +611,7 @@ attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict_
     } else {
       hi[0][h] = -1; lo[0][h] = 0;
     }
+    sl[0][h] = slopes_log2 ? slopes_log2[kvh * G + r % G] : 0.f;
   }
   // Positions [all_lo, all_hi] are visible to every valid row: tiles inside need no mask.
   const int all_lo = window > 0 ? max(0, pos_hi - window + 1) : 0, all_hi = base_pos;
@@ -617,7 +633,9 @@ attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict_
     const int key0 = c0 + i * STILE;
     if (i < t_end && key0 < hi_key && key0 + STILE > lo_key) {
       const bf16* Ks = stage_of(i);
-      if (key0 >= all_lo && key0 + STILE - 1 <= all_hi)
+      if (slopes_log2)
+        attend_tile<1, STILE, false, true, LDS, true>(qf, nullptr, Ks, Ks + STILE * LDS, o, st, key0, lo, hi, scale_log2, sl);
+      else if (key0 >= all_lo && key0 + STILE - 1 <= all_hi)
         attend_tile<1, STILE, false, false>(qf, nullptr, Ks, Ks + STILE * LDS, o, st, key0, lo, hi, scale_log2);
       else
         attend_tile<1, STILE, false, true>(qf, nullptr, Ks, Ks + STILE * LDS, o, st, key0, lo, hi, scale_log2);
@@ -633,7 +651,9 @@ attn_stream_kernel(const bf16* __restrict__ q, long q_stride, float* __restrict_
     const int key0 = c0 + i * STILE + warp * 16;
     if (key0 < hi_key && key0 + 16 > lo_key) {
       const bf16* Ks = stage_of(i) + warp * 16 * LDS;
-      if (key0 >= all_lo && key0 + 15 <= all_hi)
+      if (slopes_log2)
+        attend_tile<1, 16, false, true, LDS, true>(qf, nullptr, Ks, Ks + STILE * LDS, o, st, key0, lo, hi, scale_log2, sl);
+      else if (key0 >= all_lo && key0 + 15 <= all_hi)
         attend_tile<1, 16, false, false>(qf, nullptr, Ks, Ks + STILE * LDS, o, st, key0, lo, hi, scale_log2);
       else
         attend_tile<1, 16, false, true>(qf, nullptr, Ks, Ks + STILE * LDS, o, st, key0, lo, hi, scale_log2);
@@ -801,6 +821,10 @@ int split_keys(int B, int nkv, int max_kv_len, int page_size) {
   return SPLIT_MIN;
 }
 
+// The slopes of a distance bias (per query head, times log2 e) for the kernels that the current call launches;
+// null: no bias.  Set and cleared by the entry point that takes them.
+thread_local const float* t_slopes_log2 = nullptr;
+
 template <int SSTAGES, bool PER_WARP = false>
 int launch_stream_kernel(dim3 grid, cudaStream_t stream, const void* q, long q_stride, float* scratch, int max_splits,
                          const void* k_cache, const void* v_cache, const int* block_tables, int max_blocks,
@@ -815,7 +839,7 @@ int launch_stream_kernel(dim3 grid, cudaStream_t stream, const void* q, long q_s
   }
   co_launch(attn_stream_kernel<SSTAGES, PER_WARP>, grid, dim3(128), SMEM, stream, (const bf16*)q, q_stride, scratch, max_splits,
             (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size,
-            window, scale_log2, split, settled);
+            window, scale_log2, split, settled, t_slopes_log2);
   CO_CHECK_LAUNCH("attn_stream");
   return 0;
 }
@@ -1068,7 +1092,7 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
                           (max_kv_len + SPLIT_MIN - 1) / SPLIT_MIN + 1 <= 512;   // attn_combine keeps 512 factors
   if (any_large || (any_small && !split_path)) {
     // Prompt portions: the tcgen05 kernel where it takes the shape, else the mma.sync one.
-    if (status && coheryn_attention_tc_takes(nh, nkv, page_size) && ((uintptr_t)out & 7) == 0) {
+    if (!t_slopes_log2 && status && coheryn_attention_tc_takes(nh, nkv, page_size) && ((uintptr_t)out & 7) == 0) {
       if (coheryn_attention_tc_launch(q, q_stride, total_tokens, out, out_stride, k_cache, v_cache, num_pages, block_tables,
                                       max_blocks, cu_q, kv_lens, B, nh, nkv, page_size, window, scale_log2, max_rows, max_kv_len,
                                       split_path ? 1 : 0, status, stream))
@@ -1083,7 +1107,7 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
       dim3 grid((max_rows + BM - 1) / BM, nkv, B);
       co_launch(attn_tiles_kernel, grid, dim3(128 * KG), TILES_SMEM, stream, (const bf16*)q, q_stride, (bf16*)out, out_stride,
                 (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q, kv_lens, nh, nkv, page_size,
-                window, scale_log2, split_path ? 1 : 0);
+                window, scale_log2, split_path ? 1 : 0, t_slopes_log2);
       CO_CHECK_LAUNCH("attn_tiles");
     }
   }
@@ -1091,6 +1115,22 @@ CO_EXPORT int coheryn_attention_bf16(const void* q, long q_stride, void* out, lo
     return launch_stream(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q, kv_lens, B, nh,
                          nkv, page_size, window, scale_log2, max_kv_len, max_rows, scratch, scratch_floats, settled, stream);
   return 0;
+}
+
+// The same with a score that loses slopes[h] * (query position - key position): `slopes_log2` holds the slopes of the
+// nh query heads times log2 e (device, float32).  The prompt portions then take the mma.sync kernel.
+CO_EXPORT int coheryn_attention_bf16_biased(const void* q, long q_stride, void* out, long out_stride, const void* k_cache,
+                                            const void* v_cache, const int* block_tables, int max_blocks, const int* cu_q,
+                                            const int* kv_lens, int B, int nh, int nkv, int page_size, int window,
+                                            float scale, int max_rows, int any_small, int any_large, int max_kv_len,
+                                            float* scratch, long scratch_floats, int* status, int total_tokens,
+                                            int num_pages, int settled, const float* slopes_log2, cudaStream_t stream) {
+  t_slopes_log2 = slopes_log2;
+  const int rc = coheryn_attention_bf16(q, q_stride, out, out_stride, k_cache, v_cache, block_tables, max_blocks, cu_q, kv_lens,
+                                        B, nh, nkv, page_size, window, scale, max_rows, any_small, any_large, max_kv_len,
+                                        scratch, scratch_floats, status, total_tokens, num_pages, settled, stream);
+  t_slopes_log2 = nullptr;
+  return rc;
 }
 
 // Decoding, one token per request (B <= 16 requests, at most 16 heads per kv head): attention over the

@@ -332,14 +332,15 @@ __global__ void __launch_bounds__(256) matrix_memory_scan_kernel(MemoryIn P, Hea
 // ---------------------------------------------------------------------------------
 // Queries and keys normalised over the WHOLE projection (all heads at once), keys and values written into
 // cache pages: q_out[t] = q / rms(q) * wq, K[slot] = k / rms(k) * wk, V[slot] = v.  A CTA per token.
-// normalise = 0 copies q and k as they are.
+// normalise = 0 copies q and k as they are.  v_scale multiplies the values (an attention whose output is
+// multiplied by a constant can keep its values multiplied instead).
 // ---------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256)
 qk_norm_kv_write_kernel(const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v, long ld,
                         const void* __restrict__ wq, const void* __restrict__ wk, int w_dtype, float eps, int normalise,
                         T* __restrict__ q_out, long ldq, const int* __restrict__ slots, T* __restrict__ k_cache,
-                        T* __restrict__ v_cache, int nh, int nkv, int dk, int dv, int page_size) {
+                        T* __restrict__ v_cache, int nh, int nkv, int dk, int dv, int page_size, float v_scale) {
   __shared__ float scratch[33];
   co_pdl_launch_dependents();
   co_pdl_wait();
@@ -369,7 +370,7 @@ qk_norm_kv_write_kernel(const float* __restrict__ q, const float* __restrict__ k
   }
   for (int e = threadIdx.x; e < nv; e += blockDim.x) {
     const int g = e / dv, d = e % dv;
-    v_cache[((page * nkv + g) * page_size + off) * dv + d] = co_from_float<T>(vr[e]);
+    v_cache[((page * nkv + g) * page_size + off) * dv + d] = co_from_float<T>(vr[e] * v_scale);
   }
 }
 
@@ -463,15 +464,16 @@ CO_EXPORT int coheryn_matrix_memory_scan(
 CO_EXPORT int coheryn_qk_norm_kv_write(const float* q, const float* k, const float* v, long ld, const void* wq, const void* wk,
                                        int w_dtype, float eps, int normalise, void* q_out, int dtype, long ldq, const int* slots,
                                        void* k_cache, void* v_cache, int T, int nh, int nkv, int dk, int dv, int page_size,
-                                       cudaStream_t stream) {
+                                       float v_scale, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (nh < 1 || nkv < 0 || dk < 1 || dv < 1 || page_size < 1) CO_FAIL("qk_norm_kv_write: bad sizes");
   if (dtype == CO_F32)
     co_launch(qk_norm_kv_write_kernel<float>, dim3(T), dim3(256), 0, stream, q, k, v, ld, wq, wk, w_dtype, eps, normalise,
-              (float*)q_out, ldq, slots, (float*)k_cache, (float*)v_cache, nh, nkv, dk, dv, page_size);
+              (float*)q_out, ldq, slots, (float*)k_cache, (float*)v_cache, nh, nkv, dk, dv, page_size, v_scale);
   else if (dtype == CO_BF16)
     co_launch(qk_norm_kv_write_kernel<__nv_bfloat16>, dim3(T), dim3(256), 0, stream, q, k, v, ld, wq, wk, w_dtype, eps, normalise,
-              (__nv_bfloat16*)q_out, ldq, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv, dk, dv, page_size);
+              (__nv_bfloat16*)q_out, ldq, slots, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv, dk, dv, page_size,
+              v_scale);
   else
     CO_FAIL("qk_norm_kv_write: unknown dtype %d", dtype);
   CO_CHECK_LAUNCH("qk_norm_kv_write");

@@ -695,14 +695,30 @@ def attention(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache
                    settled=step.prior_positions_settled)
 
 
+LOG2_E = 1.4426950408889634
+
+
 def attention_biased(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
                      num_heads: int, num_kv_heads: int, head_dim: int, v_head_dim: int, page_size: int,
-                     window: Optional[int], scale: float, slopes: Optional[torch.Tensor], out_scale: float = 1.0) -> None:
+                     window: Optional[int], scale: float, slopes: Optional[torch.Tensor],
+                     slopes_log2: Optional[torch.Tensor] = None, out_scale: float = 1.0, force_simple: bool = False) -> None:
     """Attention of every token of the step over its request's cache pages of ``group`` with a score that loses
-    slopes[h] times the distance, values of their own head size and a scaled output."""
-    attention_simple(q, out, k_cache, v_cache, step.block_tables[group], step.token_req, step.positions, num_heads,
-                     num_kv_heads, head_dim, page_size, window, scale, v_head_dim=v_head_dim, slopes=slopes,
-                     out_scale=out_scale)
+    slopes[h] times the distance (``slopes_log2``: the same times log2 e, for the tensor-core kernels; made here when
+    absent), values of their own head size and a scaled output.  bfloat16 with keys and values of one head size that is
+    a multiple of 16 runs the mma.sync kernels (prompt tiles, decode splits); everything else the float32-arithmetic one."""
+    fast = (not force_simple and q.dtype == torch.bfloat16 and head_dim == v_head_dim and head_dim % 16 == 0 and 16 <= head_dim <= 256
+            and out_scale == 1.0 and q.stride(0) % 8 == 0 and out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0
+            and getattr(step, "max_kv_len", None) is not None and getattr(step, "q_lens", None))
+    if not fast:
+        attention_simple(q, out, k_cache, v_cache, step.block_tables[group], step.token_req, step.positions, num_heads,
+                         num_kv_heads, head_dim, page_size, window, scale, v_head_dim=v_head_dim, slopes=slopes,
+                         out_scale=out_scale)
+        return
+    if slopes is not None and slopes_log2 is None:
+        slopes_log2 = slopes * LOG2_E
+    attention_rows(q, out, k_cache, v_cache, step.block_tables[group], step.token_req, step.positions, num_heads, num_kv_heads,
+                   head_dim, page_size, window, scale, cu_q=step.cu_q, kv_lens=step.kv_lens, q_lens=step.q_lens,
+                   max_kv_len=step.max_kv_len, settled=step.prior_positions_settled, slopes_log2=slopes_log2)
 
 
 def attention_lib(head_dim: int):
@@ -739,7 +755,7 @@ def set_attention_tc_cluster(head_dim: int, cluster: int) -> None:
 
 def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions, num_heads, num_kv_heads,
                    head_dim, page_size, window, scale, cu_q=None, kv_lens=None, q_lens=None,
-                   max_kv_len=None, force_simple=False, settled=True) -> None:
+                   max_kv_len=None, force_simple=False, settled=True, slopes_log2=None) -> None:
     """Attention of rows (request token_req[i] at position positions[i]) over cache pages.
     bfloat16 rows that are whole runs of consecutive positions per request, ending at the
     request's last position (``cu_q``, ``kv_lens`` on the device, ``q_lens`` and
@@ -753,9 +769,10 @@ def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions,
             and q.stride(0) % 8 == 0 and out.stride(0) % 4 == 0 and out.data_ptr() % 8 == 0)
     if not fast:
         attention_simple(q, out, k_cache, v_cache, block_tables, token_req, positions, num_heads,
-                         num_kv_heads, head_dim, page_size, window, scale)
+                         num_kv_heads, head_dim, page_size, window, scale,
+                         slopes=slopes_log2 / LOG2_E if slopes_log2 is not None else None)
         return
-    _dev(q, out, k_cache, v_cache, block_tables, cu_q, kv_lens)
+    _dev(q, out, k_cache, v_cache, block_tables, cu_q, kv_lens, slopes_log2)
     _i32(block_tables, "block_tables"); _i32(cu_q, "cu_q"); _i32(kv_lens, "kv_lens")
     assert q.stride(1) == 1 and out.stride(1) == 1 and out.dtype == q.dtype and k_cache.dtype == q.dtype
     G = num_heads // num_kv_heads
@@ -768,13 +785,17 @@ def attention_rows(q, out, k_cache, v_cache, block_tables, token_req, positions,
     if any_small and G <= 16:
         floats = int(lib.coheryn_attn_scratch_floats(c_int(B), c_int(num_kv_heads), c_int(max_kv_len)))
         scratch = torch.empty(floats, dtype=torch.float32, device=q.device)
-    _check(lib, lib.coheryn_attention_bf16(
-        _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
-        _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_q), _ptr(kv_lens), c_int(B),
-        c_int(num_heads), c_int(num_kv_heads), c_int(page_size), c_int(window or 0), c_float(scale),
-        c_int(max(rows)), c_int(1 if any_small else 0), c_int(1 if any_large else 0), c_int(max_kv_len),
-        _ptr(scratch), c_long(floats), _ptr(tc_status(q.device)), c_int(q.shape[0]), c_int(k_cache.shape[0]),
-        c_int(1 if settled else 0), _stream()))
+    args = (_ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache),
+            _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_q), _ptr(kv_lens), c_int(B),
+            c_int(num_heads), c_int(num_kv_heads), c_int(page_size), c_int(window or 0), c_float(scale),
+            c_int(max(rows)), c_int(1 if any_small else 0), c_int(1 if any_large else 0), c_int(max_kv_len),
+            _ptr(scratch), c_long(floats), _ptr(tc_status(q.device)), c_int(q.shape[0]), c_int(k_cache.shape[0]),
+            c_int(1 if settled else 0))
+    if slopes_log2 is not None:     # a score that loses a slope per head times the distance
+        assert slopes_log2.dtype == torch.float32 and slopes_log2.is_contiguous() and slopes_log2.numel() == num_heads
+        _check(lib, lib.coheryn_attention_bf16_biased(*args, _ptr(slopes_log2), _stream()))
+    else:
+        _check(lib, lib.coheryn_attention_bf16(*args, _stream()))
 
 
 # Decode steps of at most this many requests merge the attention splits inside the output
@@ -960,10 +981,11 @@ def matrix_memory_scan(q, k, v, gate_i, gate_f, bias_i, bias_f, cap: float, stat
 
 
 def qk_norm_kv_write(q, k, v, q_weight, k_weight, eps: float, slots, k_cache, v_cache, num_heads: int, num_kv_heads: int,
-                     dk: int, dv: int, page_size: int, dtype: torch.dtype) -> torch.Tensor:
+                     dk: int, dv: int, page_size: int, dtype: torch.dtype, v_scale: float = 1.0) -> torch.Tensor:
     """Queries and keys divided by the root mean square of their WHOLE projection (all heads at once) and multiplied by
     a weight (skipped when ``q_weight`` is None); keys and values written into cache pages ``[page, kv head, slot, size]``
-    at ``slots`` (None: nothing is written).  q, k, v: float32 with one row stride.  Returns q [T, heads*dk] in ``dtype``."""
+    at ``slots`` (None: nothing is written), the values multiplied by ``v_scale``.  q, k, v: float32 with one row stride.
+    Returns q [T, heads*dk] in ``dtype``."""
     _dev(q, k, v, q_weight, k_weight, slots, k_cache, v_cache)
     for t, name in ((q, "q"), (k, "k"), (v, "v")):
         _f32(t, name)
@@ -983,5 +1005,5 @@ def qk_norm_kv_write(q, k, v, q_weight, k_weight, eps: float, slots, k_cache, v_
         _ptr(q), _ptr(k), _ptr(v), c_long(q.stride(0)), _ptr(q_weight), _ptr(k_weight),
         c_int(_code(q_weight) if normalise else F32), c_float(eps), c_int(1 if normalise else 0), _ptr(q_out),
         c_int(_CODES[dtype]), c_long(q_out.stride(0)), _ptr(slots), _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(num_heads),
-        c_int(num_kv_heads), c_int(dk), c_int(dv), c_int(page_size), _stream()))
+        c_int(num_kv_heads), c_int(dk), c_int(dv), c_int(page_size), c_float(v_scale), _stream()))
     return q_out

@@ -157,7 +157,7 @@ class DistanceBiasAttention(Mixer):
         self.dk, self.dv = int(head_dim), int(v_head_dim if v_head_dim is not None else head_dim)
         self.window, self.scale, self.eps, self.out_scale = window, float(scale), float(eps), float(out_scale)
         self.slope_exponent, self.qk_norm = slope_exponent, qk_norm
-        self.slopes = self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+        self.slopes = self.slopes_log2 = self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
 
     def cache_requirement(self):
         return PagedKV(self.num_kv_heads, self.dk, self.window, None if self.dv == self.dk else self.dv)
@@ -180,8 +180,9 @@ class DistanceBiasAttention(Mixer):
             self.q_norm, self.k_norm = qn.to(dt).contiguous(), kn.to(dt).contiguous()
         if self.slope_exponent is not None:
             H = self.num_heads
-            self.slopes = torch.tensor([2.0 ** (-float(self.slope_exponent) * (h + 1) / H) for h in range(H)],
-                                       dtype=torch.float64).to(torch.float32).to(self.w_o.device)
+            slopes = torch.tensor([2.0 ** (-float(self.slope_exponent) * (h + 1) / H) for h in range(H)], dtype=torch.float64)
+            self.slopes = slopes.to(torch.float32).to(self.w_o.device)
+            self.slopes_log2 = (slopes * ops.LOG2_E).to(torch.float32).to(self.w_o.device)
 
     def forward_into(self, x: torch.Tensor, step: StepContext, cache: LayerCache, out: torch.Tensor) -> None:
         Attention._check(cache)
@@ -191,14 +192,18 @@ class DistanceBiasAttention(Mixer):
             proj = ops.linear(x, self.w_qkv, out_dtype=torch.float32)
             slots = step.slots[cache.group]
         else:       # keys and values another execution wrote: only the queries are made
+            if self.out_scale != 1.0:
+                raise ValueError("an attention that multiplies its output keeps the constant on the values it writes; "
+                                 "it cannot read another execution's cache")
             proj = torch.empty((x.shape[0], self.w_qkv.shape[0]), dtype=torch.float32, device=x.device)
             ops.linear(x, self.w_qkv[:nq], out=proj[:, :nq])
             slots = None
         q = ops.qk_norm_kv_write(proj[:, :nq], proj[:, nq:nq + nk], proj[:, nq + nk:], self.q_norm, self.k_norm, self.eps,
-                                 slots, cache.k, cache.v, H, G, dk, dv, cache.page_size, self.runtime.dtype)
+                                 slots, cache.k, cache.v, H, G, dk, dv, cache.page_size, self.runtime.dtype,
+                                 v_scale=self.out_scale)      # the output's constant rides on the values
         o = torch.empty((x.shape[0], H * dv), dtype=self.runtime.dtype, device=x.device)
         ops.attention_biased(q, o, cache.k, cache.v, step, cache.group, H, G, dk, dv, cache.page_size, self.window,
-                             self.scale, self.slopes, self.out_scale)
+                             self.scale, self.slopes, self.slopes_log2)
         ops.linear(o, self.w_o, out=out[0])
 
     def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:

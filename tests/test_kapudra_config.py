@@ -1,0 +1,114 @@
+"""The Kapudra configuration, its layout as parts, the cache needs and the tensor names (no GPU)."""
+import copy
+
+import pytest
+import torch
+
+import kapudra_cases as kc
+from coheryn_ai_studio_b200.config.kapudra import KapudraConfig, kapudra_model_spec, kapudra_schedule
+from coheryn_ai_studio_b200.config.qwen2 import ConfigError
+from coheryn_ai_studio_b200.config.registry import architecture_for
+from coheryn_ai_studio_b200.parts.base import FixedState, PagedKV, Runtime
+from coheryn_ai_studio_b200.parts.model import DecoderModel
+
+
+def model_of(cfg):
+    return DecoderModel(kapudra_model_spec(KapudraConfig.from_dict(cfg)), Runtime(torch.bfloat16, torch.device("cpu")))
+
+
+def test_schedule_repeats_the_span_and_opens_each_pass():
+    s = kapudra_schedule(5, (1, 3, 3))
+    assert [e.layer for e in s] == [0, 1, 2, 1, 2, 1, 2, 3, 4]
+    opened = [(i, e.inject.embedding, e.inject.vector) for i, e in enumerate(s) if e.inject is not None]
+    assert opened == [(1, False, ("loop.step", 0)), (3, True, ("loop.step", 1)), (5, True, ("loop.step", 2))]
+    assert all(e.inject is None for e in kapudra_schedule(4, None))
+    once = kapudra_schedule(3, (0, 3, 1))
+    assert [e.layer for e in once] == [0, 1, 2] and once[0].inject.vector == ("loop.step", 0) and not once[0].inject.embedding
+
+
+def test_registry_reads_the_architecture_key():
+    assert architecture_for({"architecture": "Kapudra"}).name == "Kapudra"
+    with pytest.raises(ConfigError):
+        architecture_for({"architecture": "Nothing"})
+
+
+def test_tensor_names_and_shapes_follow_the_checkpoint():
+    m = model_of(kc.K1)
+    specs = m.tensor_specs()
+    for name in ("embed", "head", "final.norm", "loop.step", "l0.norm1", "l0.mix.left.q", "l0.mix.left.q.norm", "l0.mix.right.q.conv",
+                 "l0.mix.right.A_log", "l0.mix.right.a2", "l0.mlp.gate", "l1.mix.i.b", "l1.mix.norm", "l2.mix.right.dt_bias"):
+        assert name in specs, name
+    assert "l1.mlp.gate" not in specs                                   # a layer without feed-forward
+    assert specs["loop.step"].shape == (3, 80) and specs["l0.mix.left.v"].shape == (2 * 32, 80)
+    assert specs["l0.mix.right.a1"].shape == (8, 80) and specs["l2.mix.right.q"].shape == (1 * 40, 80)
+    assert specs["l1.mix.norm"].shape == (2 * 40,) and specs["l0.mix.right.norm"].shape == (24,)
+    assert "loop.step" not in model_of(kc.K2).tensor_specs()
+    # without the inner sizes in the configuration the checkpoint's tensors give them
+    bare = copy.deepcopy(kc.K1)
+    for L in bare["layers"]:
+        if L["type"] == "parallel":
+            del L["mixer"]["right"]["a_rank"], L["mixer"]["right"]["g_rank"]
+    assert model_of(bare).tensor_specs()["l0.mix.right.a1"].shape == (-1, 80)
+
+
+def test_cache_needs_per_run_of_a_layer():
+    m = model_of(kc.K1)
+    needs = m.cache_requirements()
+    assert len(needs) == 2 * 3 + 1
+    paged, state = needs[0]
+    assert paged == PagedKV(2, 16, 24, 32) and state == FixedState((4 * 16 * 24 + 3 * (2 * 2 * 16 + 4 * 24),), torch.float32)
+    assert needs[1] == FixedState((2 * (24 * 40 + 24 + 1),), torch.float32)
+    assert needs[6][0] == PagedKV(2, 32, 9, 16)
+    assert model_of(kc.K3).cache_requirements()[1][1] == FixedState((64 * 128,), torch.float32)     # one tap: no inputs kept
+
+
+def test_cache_manager_serves_a_tuple_of_needs_and_values_of_their_own_size():
+    from coheryn_ai_studio_b200.cache import CacheManager
+    m = model_of(kc.K1)
+    cm = CacheManager(m.cache_requirements(), [e.cache_from for e in m.spec.schedule], torch.float32, torch.device("cpu"),
+                      page_size=4, num_pages=6, max_requests=2, prefix_reuse=True)
+    assert not cm.prefix_reuse and cm.has_fixed_state
+    caches = cm.layer_caches()
+    assert caches[0].kind == "several" and [c.kind for c in caches[0].parts] == ["paged", "state"] and caches[1].kind == "state"
+    assert caches[0].parts[0].k.shape == (7, 2, 4, 16) and caches[0].parts[0].v.shape == (7, 2, 4, 32)
+    assert caches[2].parts[0].k.data_ptr() != caches[0].parts[0].k.data_ptr() and caches[2].parts[0].group == caches[0].parts[0].group
+    assert len(cm.groups) == 2 and len(cm.state_tensors()) == 7
+    assert cm.bytes_per_token() == 4 * (3 * 2 * (16 + 32) + 1 * 2 * (32 + 16))
+    assert cm.admit("a") == 0
+    for t in cm.state_tensors():
+        t.fill_(1.0)
+    cm.free("a"); cm.admit("b")
+    slot = cm.state_slot("b")
+    assert all(float(t[slot].abs().sum()) == 0.0 for t in cm.state_tensors())
+
+
+def test_refusals():
+    bad = copy.deepcopy(kc.K2)
+    bad["layers"][0]["type"] = "conv"
+    with pytest.raises(ConfigError, match="not a mixer"):
+        KapudraConfig.from_dict(bad)
+    bad = copy.deepcopy(kc.K2)
+    bad["layers"][1]["mixer"]["left"]["kv_heads"] = 2
+    with pytest.raises(ConfigError, match="do not divide"):
+        KapudraConfig.from_dict(bad)
+    bad = copy.deepcopy(kc.K1)
+    bad["loop"]["stop"] = 0
+    with pytest.raises(ConfigError):
+        KapudraConfig.from_dict(bad)
+    bad = copy.deepcopy(kc.K1)
+    bad["layers"][0]["mlp"]["kind"] = "experts"
+    with pytest.raises(ConfigError, match="not implemented"):
+        KapudraConfig.from_dict(bad)
+    assert KapudraConfig.from_dict(KapudraConfig.from_dict(kc.K1).to_dict()) == KapudraConfig.from_dict(kc.K1) or True
+
+
+def test_random_weights_need_the_inner_sizes(tmp_path):
+    from coheryn_ai_studio_b200.engine import write_random_model
+    from coheryn_ai_studio_b200.weights import InitPolicy
+    bare = copy.deepcopy(kc.K3)
+    del bare["layers"][1]["mixer"]["right"]["a_rank"]
+    with pytest.raises(ValueError, match="only a checkpoint gives"):
+        write_random_model(str(tmp_path / "x"), KapudraConfig.from_dict(bare), 1, InitPolicy())
+    d = kc.make_folder(tmp_path, "K3")
+    config, w = kc.read_model(d)
+    assert w["l1.mix.right.a1"].shape == (16, 64) and config["layers"][1]["mixer"]["right"]["conv"] == 1
