@@ -23,7 +23,9 @@ whose prefix 8 requests share (prefill in 2,048-token portions, prefix pages reu
 decoding at batch 8.  ``--workload chat-1.5b`` is this repository's own: 256 short requests at the
 1.5B layer sizes (prompts uniform in [16, 256], 16 to 128 output tokens each, at most 32 running), so
 that requests end and begin all the time and many steps carry a new prompt beside decoded tokens,
-which no graph replays: it measures what such steps cost the host.
+which no graph replays: it measures what such steps cost the host.  ``--workload kapudra`` measures the Kapudra design
+(matrix-memory layers and attention beside a gated delta rule) at two layer sizes beside Qwen2 at equal sizes: prefill and
+decode through the step function, and the mixers' kernels alone.
 """
 from __future__ import annotations
 
@@ -226,6 +228,192 @@ def other_workload(args) -> int:
     return 0
 
 
+# Kapudra at layer sizes that resemble a real model's (random weights), beside Qwen2 at the same width, feed-forward
+# size, head counts and number of layers.  Eight layers each: matrix memory, matrix memory, and twice attention beside
+# a gated delta rule, repeated.
+KAPUDRA_SIZES = {
+    "1.5b-like": dict(width=1536, ff=4096, heads=12, kv_heads=2, head_dim=128, window=1024, state_heads=12, state_dim=128,
+                      memory_heads=8, memory_vdim=256, vocab=32000, layers=8),
+    "3b-like": dict(width=2560, ff=6912, heads=20, kv_heads=4, head_dim=128, window=2048, state_heads=16, state_dim=128,
+                    memory_heads=8, memory_vdim=256, vocab=32000, layers=8),
+}
+
+
+def kapudra_config(z):
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["head_dim"], "vdim": z["head_dim"],
+            "scale": z["head_dim"] ** -0.5, "mask": {"size": z["window"]}}
+    right = {"heads": z["state_heads"], "kv_heads": z["state_heads"], "dim": z["state_dim"], "vdim": z["state_dim"], "conv": 4,
+             "a_rank": 64, "g_rank": 64}
+    par = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0},
+           "mlp": {"kind": "dense", "ff": z["ff"]}}
+    mem = {"type": "mlstm", "mixer": {"heads": z["memory_heads"], "dim": z["state_dim"], "vdim": z["memory_vdim"], "gate_cap": 15.0},
+           "mlp": {"kind": "dense", "ff": z["ff"]}}
+    kinds = [mem, mem, par, par]
+    return {"architecture": "Kapudra", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "logit_scale": 1.0, "logit_softcap": 30.0, "layers": [kinds[i % 4] for i in range(z["layers"])]}
+
+
+def kapudra_workload(args) -> int:
+    """Prefill and decode throughput of Kapudra and of Qwen2 at equal sizes through the step function (CUDA events around
+    the steps, inputs from pinned host memory as every step has them), and the mixers' kernels alone with their share of
+    the roofline.  One JSON line."""
+    import numpy as np
+    import torch
+
+    from coheryn_ai_studio_b200 import ops
+    from coheryn_ai_studio_b200.cache import CacheManager
+    from coheryn_ai_studio_b200.config import Qwen2Config
+    from coheryn_ai_studio_b200.config.kapudra import KapudraConfig
+    from coheryn_ai_studio_b200.engine import StepEntry, StepRunner, random_model_on_device
+
+    pk = peaks()
+    hbm = pk["hbm_gbs"] * 1e9
+    flops_peak = pk.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]) * 1e12
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    tokens, batch, context, steps = args.prefill_tokens, args.batch, min(args.context, 2048), max(8, min(args.steps, 32))
+    rng = np.random.default_rng(0)
+
+    def timed(fn, repeats=5):
+        """Median of CUDA-event times of fn() with L2 flushed before each."""
+        out = []
+        for r in range(repeats + 2):
+            flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); fn(); e1.record()
+            torch.cuda.synchronize()
+            if r >= 2:
+                out.append(e0.elapsed_time(e1))
+        return float(np.median(out))
+
+    def run_model(model, vocab):
+        need = batch * (context + steps + 16) + tokens + 64
+        cache = CacheManager(model.cache_requirements(), [e.cache_from for e in model.spec.schedule], torch.bfloat16, dev,
+                             page_size=args.page_size, num_pages=-(-need // args.page_size) + batch + 1, max_requests=batch + 1,
+                             prefix_reuse=False)
+        runner = StepRunner(model, cache, use_graphs=not args.no_graphs, graph_max_kv_len=context + steps + 16)
+        best = None
+        for r in range(3):
+            cache.admit("p")
+            prompt = rng.integers(0, vocab, size=tokens).tolist()
+            torch.cuda.synchronize(); flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(); runner.step([StepEntry("p", prompt, [tokens - 1])]); e1.record()
+            torch.cuda.synchronize()
+            runner.check_status()
+            cache.free("p")
+            if r:
+                best = e0.elapsed_time(e1) if best is None else min(best, e0.elapsed_time(e1))
+        ids = [f"d{i}" for i in range(batch)]
+        for rid in ids:                      # the contexts are really computed: a recurrent state cannot be made up
+            cache.admit(rid)
+            runner.step([StepEntry(rid, rng.integers(0, vocab, size=context).tolist(), [])])
+        nxt = lambda: [StepEntry(rid, [int(rng.integers(0, vocab))], [0]) for rid in ids]
+        for _ in range(max(3, args.warmup)):
+            runner.step(nxt())
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            runner.step(nxt())
+        e1.record()
+        torch.cuda.synchronize()
+        runner.check_status()
+        ms = e0.elapsed_time(e1) / steps
+        return {"prefill_tokens_per_s": round(tokens / (best / 1e3)), "prefill_ms": round(best, 3),
+                "decode_tokens_per_s": round(batch / (ms / 1e3)), "decode_ms_per_step": round(ms, 4)}
+
+    def step_like(lengths, starts, tables=None):
+        import types
+        cu = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+        t = lambda a: torch.as_tensor(np.asarray(a, dtype=np.int32)).to(dev)
+        st = types.SimpleNamespace(
+            num_requests=len(lengths), num_tokens=int(cu[-1]), cu_q=t(cu), token_req=t(np.repeat(np.arange(len(lengths)), lengths)),
+            positions=t(np.concatenate([np.arange(s, s + n) for s, n in zip(starts, lengths)])), state_slots=t(np.arange(len(lengths))),
+            q_lens=list(lengths), kv_lens=t([s + n for s, n in zip(starts, lengths)]), max_q_len=max(lengths),
+            max_kv_len=max(s + n for s, n in zip(starts, lengths)), prior_positions_settled=True, block_tables=[tables])
+        return st
+
+    def kernels(z):
+        """The mixers' kernels alone, prompt (one request of ``tokens``) and decode (``batch`` requests at ``context``)."""
+        out = {}
+        H, G, hd, W, page = z["heads"], z["kv_heads"], z["head_dim"], z["window"], args.page_size
+        pages_per = -(-(context + 1) // page)
+        for name, lengths, starts in (("prefill", [tokens], [0]), ("decode", [1] * batch, [context] * batch)):
+            B, T = len(lengths), sum(lengths)
+            per = -(-max(s + n for s, n in zip(starts, lengths)) // page)
+            tables = torch.arange(B * per, dtype=torch.int32, device=dev).view(B, per)
+            st = step_like(lengths, starts, tables)
+            kc = torch.randn((B * per + 1, G, page, hd), device=dev).to(torch.bfloat16)
+            vc = torch.randn_like(kc)
+            q = torch.randn((T, H * hd), device=dev).to(torch.bfloat16)
+            o = torch.empty_like(q)
+            slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / H) for h in range(H)], dtype=torch.float32, device=dev)
+            seen = lambda w: sum(min(w, p + 1) for s, n in zip(starts, lengths) for p in range(s, s + n))       # keys read per head
+            for label, window, sl in (("attention_bias_window", W, slopes), ("attention_window", W, None), ("attention_full", None, None)):
+                fn = lambda: ops.attention_biased(q, o, kc, vc, st, 0, H, G, hd, hd, page, window, hd ** -0.5, sl) if sl is not None else \
+                    ops.attention_rows(q, o, kc, vc, tables, st.token_req, st.positions, H, G, hd, page, window, hd ** -0.5, cu_q=st.cu_q,
+                                       kv_lens=st.kv_lens, q_lens=st.q_lens, max_kv_len=st.max_kv_len)
+                ms = timed(fn)
+                keys = seen(window if window else 1 << 30)
+                fl = 4.0 * H * hd * keys
+                by = 2.0 * 2 * G * hd * sum(min(window or 1 << 30, s + n) for s, n in zip(starts, lengths)) + 4.0 * T * H * hd
+                out[f"{name}.{label}"] = {"ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1), "of_bf16_peak": round(fl / (ms / 1e3) / flops_peak, 4),
+                                          "of_hbm": round(by / (ms / 1e3) / hbm, 4)}
+            # the two scans: float32 inputs as the projections leave them
+            for label, heads, dk, dv in (("gated_delta_scan", z["state_heads"], z["state_dim"], z["state_dim"]),
+                                         ("matrix_memory_scan", z["memory_heads"], z["state_dim"], z["memory_vdim"])):
+                f = lambda *shape: torch.randn(shape, device=dev)
+                qkv = f(T, 2 * heads * dk + heads * dv)
+                gate, outb = f(T, heads * dv), torch.empty((T, heads * dv), dtype=torch.bfloat16, device=dev)
+                if label == "gated_delta_scan":
+                    state = torch.zeros((B, heads * dk * dv), device=dev)
+                    beta, pre, bias, rate, w = f(T, heads), f(T, heads * dk), f(heads * dk), f(heads) * 0.1, f(dv)
+                    fn = lambda: ops.gated_delta_scan(qkv[:, :heads * dk], qkv[:, heads * dk:2 * heads * dk], qkv[:, 2 * heads * dk:], beta, pre,
+                                                      bias, rate, state, st, heads, heads, dk, dv, outb, w, gate, 1e-6)
+                    fl = 8.0 * heads * dk * dv * T
+                else:
+                    state = torch.zeros((B, heads * (dk * dv + dk + 1)), device=dev)
+                    gates, bi, w = f(T, 2 * heads), f(heads), f(heads * dv)
+                    fn = lambda: ops.matrix_memory_scan(qkv[:, :heads * dk], qkv[:, heads * dk:2 * heads * dk], qkv[:, 2 * heads * dk:],
+                                                        gates[:, :heads], gates[:, heads:], bi, bi, 15.0, state, st, heads, dk, dv, outb, w, gate, 1e-6)
+                    fl = 6.0 * heads * dk * dv * T
+                ms = timed(fn)
+                by = 2.0 * state.numel() * 4 + qkv.numel() * 4 + gate.numel() * 4 + outb.numel() * 2
+                out[f"{name}.{label}"] = {"ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 2), "of_hbm": round(by / (ms / 1e3) / hbm, 4),
+                                          "of_fp32_fma_peak": round(fl / (ms / 1e3) / 75e12, 4)}
+        return out
+
+    sampler = ClockSampler()
+    sampler.start()
+    t0 = time.time()
+    results = {}
+    chosen = [n for n in KAPUDRA_SIZES if not args.sizes or n in args.sizes.split(",")]
+    for name in chosen:
+        z = KAPUDRA_SIZES[name]
+        entry = {}
+        model = random_model_on_device(KapudraConfig.from_dict(kapudra_config(z)), seed=0, dtype="bfloat16", device="cuda:0")
+        entry["kapudra"] = run_model(model, z["vocab"])
+        del model
+        torch.cuda.empty_cache()
+        qcfg = Qwen2Config(vocab_size=z["vocab"], hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=z["layers"],
+                           num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["head_dim"],
+                           max_position_embeddings=32768, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+        model = random_model_on_device(qcfg, seed=0, dtype="bfloat16", device="cuda:0")
+        entry["qwen2_equal_size"] = run_model(model, z["vocab"])
+        del model
+        torch.cuda.empty_cache()
+        entry["kernels"] = kernels(z)
+        results[name] = entry
+    clocks = ClockSampler.summary(sampler.window(t0, time.time()))
+    sampler.stop()
+    print(json.dumps({"workload": "kapudra", "dtype": "bf16", "data": "synthetic", "prefill_tokens": tokens, "decode_batch": batch,
+                      "decode_context": context, "decode_steps": steps, "peaks": pk, "clocks": clocks, "l2": "flushed before each timed kernel",
+                      "gpu_launches": ops.total_launch_count(), "sizes": results}))
+    return 0
+
+
 def timeline(args, make_engine, StepEntry, ops, torch) -> int:
     """Where a decode step's time goes, kernel by kernel, measured inside graph-replayed steps (the
     kernels overlap through programmatic dependent launch, so a kernel's own duration says little):
@@ -293,8 +481,9 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--no-graphs", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving-7b", "long-14b", "chat-1.5b"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving-7b", "long-14b", "chat-1.5b", "kapudra"],
                     help="decode: the contract's line (default); the others: see the header")
+    ap.add_argument("--sizes", default="", help="--workload kapudra: which of its sizes (comma separated; default all)")
     ap.add_argument("--timeline-raw", action="store_true", help="with --timeline: also every kernel's start and end")
     ap.add_argument("--timeline", action="store_true",
                     help="instead of the benchmark: the kernels of one graph-replayed decode step with their times "
@@ -311,6 +500,8 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload == "kapudra":
+        return kapudra_workload(args)
     if args.workload != "decode":
         return other_workload(args)
 

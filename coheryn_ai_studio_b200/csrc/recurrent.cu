@@ -11,9 +11,11 @@
 // A step is a batch of requests, each bringing a run of consecutive tokens (cu_q[r] .. cu_q[r+1]) that continues
 // from the request's state slot (state_slots[r]).  Everything that enters a recurrence is float32: the inputs are
 // the float32 outputs of the projections, gates and decays are computed here, the state lives in float32.  The
-// scan kernels give one CTA a (request, head): a thread owns one value channel, i.e. one column of S, in
-// registers, so the three updates of a token need no exchange between threads; the per-token vectors (q, k,
-// decays, gates) of a chunk of tokens are staged and prepared in shared memory by the whole CTA.  A token's result
+// scan kernels give one CTA a (request, head): SPLIT neighbouring lanes share one value channel, i.e. one column
+// of S, each holding a contiguous part of its key channels in registers, so a token costs each thread DK / SPLIT
+// steps and two small shuffle reductions (the column's dot products with k and with q, added in a fixed tree);
+// the per-token vectors (q, k, decays, gates) of a chunk of tokens are staged and prepared in shared memory by
+// the whole CTA.  A token's result
 // depends on the state and the tokens before it only, in an order of operations that is the same however the
 // sequence was cut into steps.
 #include "common.cuh"
@@ -98,12 +100,69 @@ __device__ __forceinline__ void head_out_chunk(const HeadOut& E, const float* os
     ss = co_warp_sum(ss);
     const float inv = 1.0f / sqrtf(ss / (float)dv + E.eps);
     const size_t row = (size_t)(row0 + i);
+#pragma unroll 4
     for (int c = lane; c < dv; c += 32) {
       const float w = co_load_any(E.weight, E.weight_dtype, (size_t)h * E.weight_stride + c);
       const float g = rc_sigmoid(E.gate[row * E.ldg + (size_t)h * dv + c]);
       rc_store(E.out, E.out_dtype, row * E.ldo + (size_t)h * dv + c, os[i * dvp + c] * inv * w * g * E.out_scale);
     }
   }
+}
+
+// ---------------------------------------------------------------------------------
+// How a scan's CTA is laid out.  SPLIT neighbouring lanes share CP neighbouring columns of S; each holds DP = DK / SPLIT
+// contiguous key channels of them in registers (CP * DP values).  A token then costs a thread 3 DP / 4 vector loads
+// from shared memory for 4 CP DP multiply-adds, and 2 CP shuffle reductions over SPLIT lanes, added in a fixed tree.
+// The per-token vectors lie in shared memory with each lane's part padded apart so that the SPLIT parts fall on
+// different banks.
+// ---------------------------------------------------------------------------------
+template <int DK, int SPLIT>
+struct ScanShape {
+  static constexpr int DP = DK / SPLIT;
+  static constexpr int STRIDE = DP + (((DP / 4) % 2 == 0) ? 4 : 0);   // an odd number of 16-byte units
+  static constexpr int ROW = SPLIT * STRIDE;
+  static_assert(DK % SPLIT == 0 && DP % 4 == 0, "a lane's part is a whole number of 16-byte units");
+  __device__ static __forceinline__ int at(int d) { return (d / DP) * STRIDE + d % DP; }
+};
+
+// A thread's part of S (CP columns by DP key channels) from and to the state [dk][dv]: 16-byte vectors over the
+// columns where four of them are whole and aligned, single values otherwise.
+template <int CP, int DP>
+__device__ __forceinline__ void scan_state_load(float (&S)[CP][DP], const float* __restrict__ st, int d0, int col0, int dk, int dv) {
+  if (CP == 4 && (dv & 3) == 0 && col0 + 4 <= dv && (((uintptr_t)st) & 15) == 0) {
+#pragma unroll
+    for (int d = 0; d < DP; ++d) {
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (d0 + d < dk) x = *reinterpret_cast<const float4*>(st + (size_t)(d0 + d) * dv + col0);
+      S[0][d] = x.x; S[1 % CP][d] = x.y; S[2 % CP][d] = x.z; S[3 % CP][d] = x.w;
+    }
+    return;
+  }
+#pragma unroll
+  for (int c = 0; c < CP; ++c)
+#pragma unroll
+    for (int d = 0; d < DP; ++d) S[c][d] = (d0 + d < dk && col0 + c < dv) ? st[(size_t)(d0 + d) * dv + col0 + c] : 0.f;
+}
+template <int CP, int DP>
+__device__ __forceinline__ void scan_state_store(const float (&S)[CP][DP], float* __restrict__ st, int d0, int col0, int dk, int dv) {
+  if (CP == 4 && (dv & 3) == 0 && col0 + 4 <= dv && (((uintptr_t)st) & 15) == 0) {
+#pragma unroll
+    for (int d = 0; d < DP; ++d)
+      if (d0 + d < dk) *reinterpret_cast<float4*>(st + (size_t)(d0 + d) * dv + col0) = make_float4(S[0][d], S[1 % CP][d], S[2 % CP][d], S[3 % CP][d]);
+    return;
+  }
+#pragma unroll
+  for (int c = 0; c < CP; ++c)
+#pragma unroll
+    for (int d = 0; d < DP; ++d)
+      if (d0 + d < dk && col0 + c < dv) st[(size_t)(d0 + d) * dv + col0 + c] = S[c][d];
+}
+
+template <int SPLIT>
+__device__ __forceinline__ float split_sum(float v) {
+#pragma unroll
+  for (int o = SPLIT / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
 }
 
 // ---------------------------------------------------------------------------------
@@ -120,33 +179,36 @@ struct DeltaIn {
   int heads, kv_heads, dk, dv;
 };
 
-template <int DK, int CT>
-__global__ void __launch_bounds__(256) gated_delta_scan_kernel(DeltaIn P, HeadOut E) {
+template <int DK, int CT, int SPLIT, int CP>
+__global__ void __launch_bounds__(512) gated_delta_scan_kernel(DeltaIn P, HeadOut E) {
+  using L = ScanShape<DK, SPLIT>;
+  constexpr int DP = L::DP, ROW = L::ROW;
   extern __shared__ __align__(16) float smem[];
   co_pdl_launch_dependents();
   co_pdl_wait();
-  const int r = blockIdx.x, h = blockIdx.y, col = threadIdx.x;
-  const int dk = P.dk, dv = P.dv, dvp = blockDim.x;
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int part = threadIdx.x % SPLIT, col0 = (threadIdx.x / SPLIT) * CP, d0 = part * DP;
+  const int dk = P.dk, dv = P.dv, dvp = (blockDim.x / SPLIT) * CP;
   const int start = P.cu_q[r], len = P.cu_q[r + 1] - start;
   if (len <= 0) return;
   const int g = h / (P.heads / P.kv_heads);
-  float* qs = smem;                    // [CT][DK]
-  float* ks = qs + CT * DK;            // [CT][DK]
-  float* gs = ks + CT * DK;            // [CT][DK]
-  float* vs = gs + CT * DK;            // [CT][dvp]
+  float* qs = smem;                    // [CT][ROW]
+  float* ks = qs + CT * ROW;           // [CT][ROW]
+  float* gs = ks + CT * ROW;           // [CT][ROW]
+  float* vs = gs + CT * ROW;           // [CT][dvp]
   float* os = vs + CT * dvp;           // [CT][dvp]
   float* betas = os + CT * dvp;        // [CT]
   float* S_state = P.state + (size_t)P.state_slots[r] * P.state_stride + (size_t)h * dk * dv;
-  float S[DK];
-#pragma unroll
-  for (int d = 0; d < DK; ++d) S[d] = (d < dk && col < dv) ? S_state[(size_t)d * dv + col] : 0.f;
+  float S[CP][DP];
+  scan_state_load<CP, DP>(S, S_state, d0, col0, dk, dv);
   const float rate = expf(co_load_any(P.rate_log, P.rate_log_dtype, h));
   const float q_scale = 1.0f / sqrtf((float)dk);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
 
   for (int c0 = 0; c0 < len; c0 += CT) {
     const int nt = min(CT, len - c0), row0 = start + c0;
-    for (int e = threadIdx.x; e < nt * DK; e += blockDim.x) {
+#pragma unroll 8
+    for (int e = threadIdx.x; e < nt * DK; e += blockDim.x) {      // unrolled: the loads of a thread are in flight together
       const int i = e / DK, d = e % DK;
       const size_t row = (size_t)(row0 + i);
       float qv = 0.f, kv = 0.f, gv = 1.f;
@@ -156,8 +218,10 @@ __global__ void __launch_bounds__(256) gated_delta_scan_kernel(DeltaIn P, HeadOu
         const float z = P.step[row * P.ld_step + (size_t)h * dk + d] + co_load_any(P.step_bias, P.step_bias_dtype, (size_t)h * dk + d);
         gv = expf(-rate * rc_softplus(z));
       }
-      qs[e] = qv; ks[e] = kv; gs[e] = gv;
+      const int o = i * ROW + L::at(d);
+      qs[o] = qv; ks[o] = kv; gs[o] = gv;
     }
+#pragma unroll 8
     for (int e = threadIdx.x; e < nt * dvp; e += blockDim.x) {
       const int i = e / dvp, c = e % dvp;
       vs[e] = c < dv ? P.v[(size_t)(row0 + i) * P.ld_qkv + (size_t)h * dv + c] : 0.f;
@@ -167,45 +231,59 @@ __global__ void __launch_bounds__(256) gated_delta_scan_kernel(DeltaIn P, HeadOu
     // q and k become unit vectors (q also divided by sqrt(dk)): a warp per token
     for (int i = warp; i < nt; i += warps) {
       float sq = 0.f, sk = 0.f;
-      for (int d = lane; d < DK; d += 32) { sq = fmaf(qs[i * DK + d], qs[i * DK + d], sq); sk = fmaf(ks[i * DK + d], ks[i * DK + d], sk); }
+      for (int d = lane; d < DK; d += 32) {
+        const float a = qs[i * ROW + L::at(d)], b = ks[i * ROW + L::at(d)];
+        sq = fmaf(a, a, sq); sk = fmaf(b, b, sk);
+      }
       sq = co_warp_sum(sq); sk = co_warp_sum(sk);
       const float iq = q_scale / sqrtf(sq + 1e-6f), ik = 1.0f / sqrtf(sk + 1e-6f);
-      for (int d = lane; d < DK; d += 32) { qs[i * DK + d] *= iq; ks[i * DK + d] *= ik; }
+      for (int d = lane; d < DK; d += 32) { qs[i * ROW + L::at(d)] *= iq; ks[i * ROW + L::at(d)] *= ik; }
     }
     __syncthreads();
     for (int i = 0; i < nt; ++i) {
-      const float4* k4 = reinterpret_cast<const float4*>(ks + i * DK);
-      const float4* g4 = reinterpret_cast<const float4*>(gs + i * DK);
-      const float4* q4 = reinterpret_cast<const float4*>(qs + i * DK);
-      float dot = 0.f;
+      const float4* k4 = reinterpret_cast<const float4*>(ks + i * ROW + part * L::STRIDE);
+      const float4* g4 = reinterpret_cast<const float4*>(gs + i * ROW + part * L::STRIDE);
+      const float4* q4 = reinterpret_cast<const float4*>(qs + i * ROW + part * L::STRIDE);
+      float dot[CP][2];
 #pragma unroll
-      for (int d = 0; d < DK / 4; ++d) {
+      for (int c = 0; c < CP; ++c) dot[c][0] = dot[c][1] = 0.f;
+#pragma unroll
+      for (int d = 0; d < DP / 4; ++d) {
         const float4 gg = g4[d], kk = k4[d];
-        S[4 * d] *= gg.x; S[4 * d + 1] *= gg.y; S[4 * d + 2] *= gg.z; S[4 * d + 3] *= gg.w;
-        dot = fmaf(S[4 * d], kk.x, dot); dot = fmaf(S[4 * d + 1], kk.y, dot);
-        dot = fmaf(S[4 * d + 2], kk.z, dot); dot = fmaf(S[4 * d + 3], kk.w, dot);
-      }
-      const float u = betas[i] * (vs[i * dvp + col] - dot);
-      float o = 0.f;
 #pragma unroll
-      for (int d = 0; d < DK / 4; ++d) {
-        const float4 kk = k4[d], qq = q4[d];
-        S[4 * d] = fmaf(kk.x, u, S[4 * d]); S[4 * d + 1] = fmaf(kk.y, u, S[4 * d + 1]);
-        S[4 * d + 2] = fmaf(kk.z, u, S[4 * d + 2]); S[4 * d + 3] = fmaf(kk.w, u, S[4 * d + 3]);
-        o = fmaf(S[4 * d], qq.x, o); o = fmaf(S[4 * d + 1], qq.y, o);
-        o = fmaf(S[4 * d + 2], qq.z, o); o = fmaf(S[4 * d + 3], qq.w, o);
+        for (int c = 0; c < CP; ++c) {
+          S[c][4 * d] *= gg.x; S[c][4 * d + 1] *= gg.y; S[c][4 * d + 2] *= gg.z; S[c][4 * d + 3] *= gg.w;
+          dot[c][0] = fmaf(S[c][4 * d], kk.x, dot[c][0]); dot[c][1] = fmaf(S[c][4 * d + 1], kk.y, dot[c][1]);
+          dot[c][0] = fmaf(S[c][4 * d + 2], kk.z, dot[c][0]); dot[c][1] = fmaf(S[c][4 * d + 3], kk.w, dot[c][1]);
+        }
       }
-      os[i * dvp + col] = o;
+      float u[CP];
+#pragma unroll
+      for (int c = 0; c < CP; ++c) u[c] = betas[i] * (vs[i * dvp + col0 + c] - split_sum<SPLIT>(dot[c][0] + dot[c][1]));
+#pragma unroll
+      for (int c = 0; c < CP; ++c) dot[c][0] = dot[c][1] = 0.f;
+#pragma unroll
+      for (int d = 0; d < DP / 4; ++d) {
+        const float4 kk = k4[d], qq = q4[d];
+#pragma unroll
+        for (int c = 0; c < CP; ++c) {
+          S[c][4 * d] = fmaf(kk.x, u[c], S[c][4 * d]); S[c][4 * d + 1] = fmaf(kk.y, u[c], S[c][4 * d + 1]);
+          S[c][4 * d + 2] = fmaf(kk.z, u[c], S[c][4 * d + 2]); S[c][4 * d + 3] = fmaf(kk.w, u[c], S[c][4 * d + 3]);
+          dot[c][0] = fmaf(S[c][4 * d], qq.x, dot[c][0]); dot[c][1] = fmaf(S[c][4 * d + 1], qq.y, dot[c][1]);
+          dot[c][0] = fmaf(S[c][4 * d + 2], qq.z, dot[c][0]); dot[c][1] = fmaf(S[c][4 * d + 3], qq.w, dot[c][1]);
+        }
+      }
+#pragma unroll
+      for (int c = 0; c < CP; ++c) {
+        const float o = split_sum<SPLIT>(dot[c][0] + dot[c][1]);
+        if (part == 0) os[i * dvp + col0 + c] = o;
+      }
     }
     __syncthreads();
     head_out_chunk(E, os, dvp, dv, nt, row0, h);
     __syncthreads();
   }
-  if (col < dv) {
-#pragma unroll
-    for (int d = 0; d < DK; ++d)
-      if (d < dk) S_state[(size_t)d * dv + col] = S[d];
-  }
+  scan_state_store<CP, DP>(S, S_state, d0, col0, dk, dv);
 }
 
 // ---------------------------------------------------------------------------------
@@ -221,18 +299,21 @@ struct MemoryIn {
   int heads, dk, dv;
 };
 
-template <int DK, int CT>
-__global__ void __launch_bounds__(256) matrix_memory_scan_kernel(MemoryIn P, HeadOut E) {
+template <int DK, int CT, int SPLIT, int CP>
+__global__ void __launch_bounds__(512) matrix_memory_scan_kernel(MemoryIn P, HeadOut E) {
+  using L = ScanShape<DK, SPLIT>;
+  constexpr int DP = L::DP, ROW = L::ROW;
   extern __shared__ __align__(16) float smem[];
   co_pdl_launch_dependents();
   co_pdl_wait();
-  const int r = blockIdx.x, h = blockIdx.y, col = threadIdx.x;
-  const int dk = P.dk, dv = P.dv, dvp = blockDim.x;
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int part = threadIdx.x % SPLIT, col0 = (threadIdx.x / SPLIT) * CP, d0 = part * DP;
+  const int dk = P.dk, dv = P.dv, dvp = (blockDim.x / SPLIT) * CP;
   const int start = P.cu_q[r], len = P.cu_q[r + 1] - start;
   if (len <= 0) return;
-  float* qs = smem;                    // [CT][DK]
-  float* ks = qs + CT * DK;            // [CT][DK]
-  float* vs = ks + CT * DK;            // [CT][dvp]
+  float* qs = smem;                    // [CT][ROW]
+  float* ks = qs + CT * ROW;           // [CT][ROW]
+  float* vs = ks + CT * ROW;           // [CT][dvp]
   float* os = vs + CT * dvp;           // [CT][dvp]
   float* li = os + CT * dvp;           // [CT] log input gate, then b = exp(i - m)
   float* lf = li + CT;                 // [CT] log forget gate, then a = exp(f + m' - m)
@@ -241,9 +322,8 @@ __global__ void __launch_bounds__(256) matrix_memory_scan_kernel(MemoryIn P, Hea
   float* S_state = slot + (size_t)h * dk * dv;
   float* n_state = slot + (size_t)P.heads * dk * dv + (size_t)h * dk;
   float* m_state = slot + (size_t)P.heads * dk * dv + (size_t)P.heads * dk + h;
-  float S[DK];
-#pragma unroll
-  for (int d = 0; d < DK; ++d) S[d] = (d < dk && col < dv) ? S_state[(size_t)d * dv + col] : 0.f;
+  float S[CP][DP];
+  scan_state_load<CP, DP>(S, S_state, d0, col0, dk, dv);
   constexpr int NJ = (DK + 31) / 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float nreg[NJ];                      // warp 0: lane holds n[lane + 32 j]
@@ -258,12 +338,15 @@ __global__ void __launch_bounds__(256) matrix_memory_scan_kernel(MemoryIn P, Hea
 
   for (int c0 = 0; c0 < len; c0 += CT) {
     const int nt = min(CT, len - c0), row0 = start + c0;
-    for (int e = threadIdx.x; e < nt * DK; e += blockDim.x) {
+#pragma unroll 8
+    for (int e = threadIdx.x; e < nt * DK; e += blockDim.x) {      // unrolled: the loads of a thread are in flight together
       const int i = e / DK, d = e % DK;
       const size_t row = (size_t)(row0 + i);
-      qs[e] = d < dk ? P.q[row * P.ld + (size_t)h * dk + d] * q_scale : 0.f;
-      ks[e] = d < dk ? P.k[row * P.ld + (size_t)h * dk + d] : 0.f;
+      const int o = i * ROW + L::at(d);
+      qs[o] = d < dk ? P.q[row * P.ld + (size_t)h * dk + d] * q_scale : 0.f;
+      ks[o] = d < dk ? P.k[row * P.ld + (size_t)h * dk + d] : 0.f;
     }
+#pragma unroll 8
     for (int e = threadIdx.x; e < nt * dvp; e += blockDim.x) {
       const int i = e / dvp, c = e % dvp;
       vs[e] = c < dv ? P.v[(size_t)(row0 + i) * P.ld + (size_t)h * dv + c] : 0.f;
@@ -282,45 +365,50 @@ __global__ void __launch_bounds__(256) matrix_memory_scan_kernel(MemoryIn P, Hea
         const float m_new = fmaxf(f + m, in);
         const float a = expf(f + m - m_new), b = expf(in - m_new);
         m = m_new;
-        float part = 0.f;
+        float sum = 0.f;
 #pragma unroll
         for (int j = 0; j < NJ; ++j) {
           const int d = lane + 32 * j;
           if (d < DK) {
-            nreg[j] = fmaf(b, ks[i * DK + d], a * nreg[j]);
-            part = fmaf(nreg[j], qs[i * DK + d], part);
+            nreg[j] = fmaf(b, ks[i * ROW + L::at(d)], a * nreg[j]);
+            sum = fmaf(nreg[j], qs[i * ROW + L::at(d)], sum);
           }
         }
-        part = co_warp_sum(part);
+        sum = co_warp_sum(sum);
         __syncwarp();
-        if (lane == 0) { lf[i] = a; li[i] = b; den[i] = fmaxf(fabsf(part), expf(-m)) + 1e-6f; }
+        if (lane == 0) { lf[i] = a; li[i] = b; den[i] = fmaxf(fabsf(sum), expf(-m)) + 1e-6f; }
       }
     }
     __syncthreads();
     for (int i = 0; i < nt; ++i) {
-      const float4* k4 = reinterpret_cast<const float4*>(ks + i * DK);
-      const float4* q4 = reinterpret_cast<const float4*>(qs + i * DK);
-      const float a = lf[i], bv = li[i] * vs[i * dvp + col];
-      float o = 0.f;
+      const float4* k4 = reinterpret_cast<const float4*>(ks + i * ROW + part * L::STRIDE);
+      const float4* q4 = reinterpret_cast<const float4*>(qs + i * ROW + part * L::STRIDE);
+      const float a = lf[i];
+      float bv[CP], o[CP][2];
 #pragma unroll
-      for (int d = 0; d < DK / 4; ++d) {
+      for (int c = 0; c < CP; ++c) { bv[c] = li[i] * vs[i * dvp + col0 + c]; o[c][0] = o[c][1] = 0.f; }
+#pragma unroll
+      for (int d = 0; d < DP / 4; ++d) {
         const float4 kk = k4[d], qq = q4[d];
-        S[4 * d] = fmaf(bv, kk.x, a * S[4 * d]); S[4 * d + 1] = fmaf(bv, kk.y, a * S[4 * d + 1]);
-        S[4 * d + 2] = fmaf(bv, kk.z, a * S[4 * d + 2]); S[4 * d + 3] = fmaf(bv, kk.w, a * S[4 * d + 3]);
-        o = fmaf(S[4 * d], qq.x, o); o = fmaf(S[4 * d + 1], qq.y, o);
-        o = fmaf(S[4 * d + 2], qq.z, o); o = fmaf(S[4 * d + 3], qq.w, o);
+#pragma unroll
+        for (int c = 0; c < CP; ++c) {
+          S[c][4 * d] = fmaf(bv[c], kk.x, a * S[c][4 * d]); S[c][4 * d + 1] = fmaf(bv[c], kk.y, a * S[c][4 * d + 1]);
+          S[c][4 * d + 2] = fmaf(bv[c], kk.z, a * S[c][4 * d + 2]); S[c][4 * d + 3] = fmaf(bv[c], kk.w, a * S[c][4 * d + 3]);
+          o[c][0] = fmaf(S[c][4 * d], qq.x, o[c][0]); o[c][1] = fmaf(S[c][4 * d + 1], qq.y, o[c][1]);
+          o[c][0] = fmaf(S[c][4 * d + 2], qq.z, o[c][0]); o[c][1] = fmaf(S[c][4 * d + 3], qq.w, o[c][1]);
+        }
       }
-      os[i * dvp + col] = o / den[i];
+#pragma unroll
+      for (int c = 0; c < CP; ++c) {
+        const float y = split_sum<SPLIT>(o[c][0] + o[c][1]);
+        if (part == 0) os[i * dvp + col0 + c] = y / den[i];
+      }
     }
     __syncthreads();
     head_out_chunk(E, os, dvp, dv, nt, row0, h);
     __syncthreads();
   }
-  if (col < dv) {
-#pragma unroll
-    for (int d = 0; d < DK; ++d)
-      if (d < dk) S_state[(size_t)d * dv + col] = S[d];
-  }
+  scan_state_store<CP, DP>(S, S_state, d0, col0, dk, dv);
   if (warp == 0) {
 #pragma unroll
     for (int j = 0; j < NJ; ++j)
@@ -374,7 +462,11 @@ qk_norm_kv_write_kernel(const float* __restrict__ q, const float* __restrict__ k
   }
 }
 
-constexpr int chunk_tokens(int DK) { return DK <= 128 ? 16 : 8; }
+constexpr int chunk_tokens(int DK) { return DK <= 128 ? 32 : 16; }
+// Lanes per group of columns and columns per group: eight lanes over four columns from 64 key channels on (a thread
+// then holds DK / 2 values of S), four lanes over two columns below.
+constexpr int scan_split(int DK) { return DK >= 64 ? 8 : 4; }
+constexpr int scan_columns(int DK) { return DK >= 64 ? 4 : 2; }
 
 }  // namespace
 
@@ -421,12 +513,12 @@ CO_EXPORT int coheryn_gated_delta_scan(
   DeltaIn P{q, k, v, ld_qkv, beta, ld_beta, step, ld_step, step_bias, step_bias_dtype, rate_log, rate_log_dtype, state,
             state_stride, cu_q, state_slots, heads, kv_heads, dk, dv};
   HeadOut E{out, out_dtype, ldo, weight, weight_dtype, weight_stride, gate, ldg, eps, out_scale};
-  const int threads = (dv + 31) / 32 * 32;
 #define LAUNCH(D)                                                                                              \
   {                                                                                                            \
-    constexpr int CT = chunk_tokens(D);                                                                        \
-    const size_t smem = ((size_t)3 * CT * D + (size_t)2 * CT * threads + CT) * sizeof(float);                  \
-    auto kern = gated_delta_scan_kernel<D, CT>;                                                                \
+    constexpr int CT = chunk_tokens(D), SP = scan_split(D), CP = scan_columns(D), ROW = ScanShape<D, SP>::ROW;  \
+    const int threads = ((dv + CP - 1) / CP * SP + 31) / 32 * 32, dvp = threads / SP * CP;                     \
+    const size_t smem = ((size_t)3 * CT * ROW + (size_t)2 * CT * dvp + CT) * sizeof(float);                                                               \
+    auto kern = gated_delta_scan_kernel<D, CT, SP, CP>;                                                                          \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
     co_launch_ex(true, kern, dim3(B, heads), dim3(threads), smem, stream, P, E);                               \
   }
@@ -446,12 +538,12 @@ CO_EXPORT int coheryn_matrix_memory_scan(
   if (!(cap > 0.f)) CO_FAIL("matrix_memory_scan: the gate cap must be positive");
   MemoryIn P{q, k, v, ld, gi, gf, ld_gate, bias_i, bias_f, bias_dtype, cap, state, state_stride, cu_q, state_slots, heads, dk, dv};
   HeadOut E{out, out_dtype, ldo, weight, weight_dtype, weight_stride, gate, ldg, eps, out_scale};
-  const int threads = (dv + 31) / 32 * 32;
 #define LAUNCH(D)                                                                                              \
   {                                                                                                            \
-    constexpr int CT = chunk_tokens(D);                                                                        \
-    const size_t smem = ((size_t)2 * CT * D + (size_t)2 * CT * threads + 3 * CT) * sizeof(float);              \
-    auto kern = matrix_memory_scan_kernel<D, CT>;                                                              \
+    constexpr int CT = chunk_tokens(D), SP = scan_split(D), CP = scan_columns(D), ROW = ScanShape<D, SP>::ROW;  \
+    const int threads = ((dv + CP - 1) / CP * SP + 31) / 32 * 32, dvp = threads / SP * CP;                     \
+    const size_t smem = ((size_t)2 * CT * ROW + (size_t)2 * CT * dvp + 3 * CT) * sizeof(float);                                                               \
+    auto kern = matrix_memory_scan_kernel<D, CT, SP, CP>;                                                                          \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
     co_launch_ex(true, kern, dim3(B, heads), dim3(threads), smem, stream, P, E);                               \
   }

@@ -145,7 +145,13 @@ class GatedDeltaRule(_StateMixer):
         convs = [tensors["q.conv"], tensors["k.conv"], tensors["v.conv"]]
         dt = torch.float32 if any(c.dtype == torch.float32 for c in convs) else convs[0].dtype
         self.conv_w = torch.cat([c.to(dt) for c in convs], dim=0).contiguous()
-        self.w_a2, self.w_g2, self.w_o = tensors["a2"], tensors["g2"], tensors["o"]
+        # The second steps of the two low-rank projections as ONE product: [a1 h | g1 h] (neighbours in the stacked
+        # output) times the block-diagonal matrix of a2 and g2 (exact zeros elsewhere) gives [step | gate].
+        a2, g2 = tensors["a2"], tensors["g2"]
+        both = torch.zeros((a2.shape[0] + g2.shape[0], a2.shape[1] + g2.shape[1]), dtype=a2.dtype, device=a2.device)
+        both[:a2.shape[0], :a2.shape[1]] = a2
+        both[a2.shape[0]:, a2.shape[1]:] = g2
+        self.w_second, self.w_o = both.contiguous(), tensors["o"]
         self.rate_log, self.dt_bias, self.norm_w = tensors["A_log"], tensors["dt_bias"], tensors["norm"]
 
     def forward_into(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], out: torch.Tensor) -> None:
@@ -153,8 +159,8 @@ class GatedDeltaRule(_StateMixer):
         st, proj = self.stacked, self.stacked.project(x)
         G, H, dk, dv = self.num_kv_heads, self.num_heads, self.dk, self.dv
         qkv = ops.short_conv_silu(st.cut(proj, "q", "v"), self.conv_w, state[:, self.memory:], step)
-        step_pre = ops.linear(st.cut(proj, "a1"), self.w_a2, out_dtype=torch.float32)
-        gate = ops.linear(st.cut(proj, "g1"), self.w_g2, out_dtype=torch.float32)
+        second = ops.linear(st.cut(proj, "a1", "g1"), self.w_second, out_dtype=torch.float32)
+        step_pre, gate = second[:, :H * dk], second[:, H * dk:]
         o = torch.empty((x.shape[0], H * dv), dtype=self.runtime.dtype, device=x.device)
         ops.gated_delta_scan(qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], st.cut(proj, "b"), step_pre,
                              self.dt_bias, self.rate_log, state[:, :self.memory], step, H, G, dk, dv, o, self.norm_w, gate,
