@@ -129,13 +129,15 @@ struct ScanShape {
 // columns where four of them are whole and aligned, single values otherwise.
 template <int CP, int DP>
 __device__ __forceinline__ void scan_state_load(float (&S)[CP][DP], const float* __restrict__ st, int d0, int col0, int dk, int dv) {
-  if (CP == 4 && (dv & 3) == 0 && col0 + 4 <= dv && (((uintptr_t)st) & 15) == 0) {
+  if (CP % 4 == 0 && (dv & 3) == 0 && col0 + CP <= dv && (((uintptr_t)st) & 15) == 0) {
 #pragma unroll
-    for (int d = 0; d < DP; ++d) {
-      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-      if (d0 + d < dk) x = *reinterpret_cast<const float4*>(st + (size_t)(d0 + d) * dv + col0);
-      S[0][d] = x.x; S[1 % CP][d] = x.y; S[2 % CP][d] = x.z; S[3 % CP][d] = x.w;
-    }
+    for (int d = 0; d < DP; ++d)
+#pragma unroll
+      for (int c = 0; c + 3 < CP; c += 4) {
+        float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (d0 + d < dk) x = *reinterpret_cast<const float4*>(st + (size_t)(d0 + d) * dv + col0 + c);
+        S[c][d] = x.x; S[c + 1][d] = x.y; S[c + 2][d] = x.z; S[c + 3][d] = x.w;
+      }
     return;
   }
 #pragma unroll
@@ -145,10 +147,13 @@ __device__ __forceinline__ void scan_state_load(float (&S)[CP][DP], const float*
 }
 template <int CP, int DP>
 __device__ __forceinline__ void scan_state_store(const float (&S)[CP][DP], float* __restrict__ st, int d0, int col0, int dk, int dv) {
-  if (CP == 4 && (dv & 3) == 0 && col0 + 4 <= dv && (((uintptr_t)st) & 15) == 0) {
+  if (CP % 4 == 0 && (dv & 3) == 0 && col0 + CP <= dv && (((uintptr_t)st) & 15) == 0) {
 #pragma unroll
     for (int d = 0; d < DP; ++d)
-      if (d0 + d < dk) *reinterpret_cast<float4*>(st + (size_t)(d0 + d) * dv + col0) = make_float4(S[0][d], S[1 % CP][d], S[2 % CP][d], S[3 % CP][d]);
+#pragma unroll
+      for (int c = 0; c + 3 < CP; c += 4)
+        if (d0 + d < dk)
+          *reinterpret_cast<float4*>(st + (size_t)(d0 + d) * dv + col0 + c) = make_float4(S[c][d], S[c + 1][d], S[c + 2][d], S[c + 3][d]);
     return;
   }
 #pragma unroll
@@ -156,6 +161,12 @@ __device__ __forceinline__ void scan_state_store(const float (&S)[CP][DP], float
 #pragma unroll
     for (int d = 0; d < DP; ++d)
       if (d0 + d < dk && col0 + c < dv) st[(size_t)(d0 + d) * dv + col0 + c] = S[c][d];
+}
+
+template <int DP>
+__device__ __forceinline__ void scan_fetch(float4 (&r)[DP / 4], const float* from) {
+#pragma unroll
+  for (int d = 0; d < DP / 4; ++d) r[d] = reinterpret_cast<const float4*>(from)[d];
 }
 
 template <int SPLIT>
@@ -240,16 +251,22 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(DeltaIn P, HeadOu
       for (int d = lane; d < DK; d += 32) { qs[i * ROW + L::at(d)] *= iq; ks[i * ROW + L::at(d)] *= ik; }
     }
     __syncthreads();
+    // The vectors of token i + 1 are fetched into registers before token i is worked on: the stores of a token's
+    // outputs would otherwise hold the next token's loads back.
+    float4 kc[DP / 4], gc[DP / 4], qc[DP / 4];
+    scan_fetch<DP>(kc, ks + part * L::STRIDE);
+    scan_fetch<DP>(gc, gs + part * L::STRIDE);
+    scan_fetch<DP>(qc, qs + part * L::STRIDE);
     for (int i = 0; i < nt; ++i) {
-      const float4* k4 = reinterpret_cast<const float4*>(ks + i * ROW + part * L::STRIDE);
-      const float4* g4 = reinterpret_cast<const float4*>(gs + i * ROW + part * L::STRIDE);
-      const float4* q4 = reinterpret_cast<const float4*>(qs + i * ROW + part * L::STRIDE);
+      float4 kn[DP / 4], gn[DP / 4], qn[DP / 4];
+      const int nx = min(i + 1, nt - 1) * ROW + part * L::STRIDE;
+      scan_fetch<DP>(kn, ks + nx); scan_fetch<DP>(gn, gs + nx); scan_fetch<DP>(qn, qs + nx);
       float dot[CP][2];
 #pragma unroll
       for (int c = 0; c < CP; ++c) dot[c][0] = dot[c][1] = 0.f;
 #pragma unroll
       for (int d = 0; d < DP / 4; ++d) {
-        const float4 gg = g4[d], kk = k4[d];
+        const float4 gg = gc[d], kk = kc[d];
 #pragma unroll
         for (int c = 0; c < CP; ++c) {
           S[c][4 * d] *= gg.x; S[c][4 * d + 1] *= gg.y; S[c][4 * d + 2] *= gg.z; S[c][4 * d + 3] *= gg.w;
@@ -264,7 +281,7 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(DeltaIn P, HeadOu
       for (int c = 0; c < CP; ++c) dot[c][0] = dot[c][1] = 0.f;
 #pragma unroll
       for (int d = 0; d < DP / 4; ++d) {
-        const float4 kk = k4[d], qq = q4[d];
+        const float4 kk = kc[d], qq = qc[d];
 #pragma unroll
         for (int c = 0; c < CP; ++c) {
           S[c][4 * d] = fmaf(kk.x, u[c], S[c][4 * d]); S[c][4 * d + 1] = fmaf(kk.y, u[c], S[c][4 * d + 1]);
@@ -278,6 +295,8 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(DeltaIn P, HeadOu
         const float o = split_sum<SPLIT>(dot[c][0] + dot[c][1]);
         if (part == 0) os[i * dvp + col0 + c] = o;
       }
+#pragma unroll
+      for (int d = 0; d < DP / 4; ++d) { kc[d] = kn[d]; gc[d] = gn[d]; qc[d] = qn[d]; }
     }
     __syncthreads();
     head_out_chunk(E, os, dvp, dv, nt, row0, h);
@@ -380,16 +399,20 @@ __global__ void __launch_bounds__(512) matrix_memory_scan_kernel(MemoryIn P, Hea
       }
     }
     __syncthreads();
+    float4 kc[DP / 4], qc[DP / 4];        // token i + 1 is fetched before token i is worked on (see the delta rule)
+    scan_fetch<DP>(kc, ks + part * L::STRIDE);
+    scan_fetch<DP>(qc, qs + part * L::STRIDE);
     for (int i = 0; i < nt; ++i) {
-      const float4* k4 = reinterpret_cast<const float4*>(ks + i * ROW + part * L::STRIDE);
-      const float4* q4 = reinterpret_cast<const float4*>(qs + i * ROW + part * L::STRIDE);
+      float4 kn[DP / 4], qn[DP / 4];
+      const int nx = min(i + 1, nt - 1) * ROW + part * L::STRIDE;
+      scan_fetch<DP>(kn, ks + nx); scan_fetch<DP>(qn, qs + nx);
       const float a = lf[i];
       float bv[CP], o[CP][2];
 #pragma unroll
       for (int c = 0; c < CP; ++c) { bv[c] = li[i] * vs[i * dvp + col0 + c]; o[c][0] = o[c][1] = 0.f; }
 #pragma unroll
       for (int d = 0; d < DP / 4; ++d) {
-        const float4 kk = k4[d], qq = q4[d];
+        const float4 kk = kc[d], qq = qc[d];
 #pragma unroll
         for (int c = 0; c < CP; ++c) {
           S[c][4 * d] = fmaf(bv[c], kk.x, a * S[c][4 * d]); S[c][4 * d + 1] = fmaf(bv[c], kk.y, a * S[c][4 * d + 1]);
@@ -403,6 +426,8 @@ __global__ void __launch_bounds__(512) matrix_memory_scan_kernel(MemoryIn P, Hea
         const float y = split_sum<SPLIT>(o[c][0] + o[c][1]);
         if (part == 0) os[i * dvp + col0 + c] = y / den[i];
       }
+#pragma unroll
+      for (int d = 0; d < DP / 4; ++d) { kc[d] = kn[d]; qc[d] = qn[d]; }
     }
     __syncthreads();
     head_out_chunk(E, os, dvp, dv, nt, row0, h);
@@ -463,10 +488,12 @@ qk_norm_kv_write_kernel(const float* __restrict__ q, const float* __restrict__ k
 }
 
 constexpr int chunk_tokens(int DK) { return DK <= 128 ? 32 : 16; }
-// Lanes per group of columns and columns per group: eight lanes over four columns from 64 key channels on (a thread
-// then holds DK / 2 values of S), four lanes over two columns below.
-constexpr int scan_split(int DK) { return DK >= 64 ? 8 : 4; }
-constexpr int scan_columns(int DK) { return DK >= 64 ? 4 : 2; }
+// Lanes per group of columns and columns per group.  The more lanes share a column, the fewer steps a token costs
+// each of them (the recurrence is a chain of dependent steps, and that chain is what bounds a long prompt): sixteen
+// from 128 key channels on, eight from 64, four below.  Four columns per group (two for narrow heads); a head of more
+// than 128 value channels takes twice as many so that the CTA stays within 512 threads.
+constexpr int scan_split(int DK) { return DK >= 128 ? 16 : (DK >= 64 ? 8 : 4); }
+constexpr int scan_columns(int DK, bool wide) { return (DK >= 64 ? 4 : 2) * (wide ? 2 : 1); }
 
 }  // namespace
 
@@ -513,17 +540,19 @@ CO_EXPORT int coheryn_gated_delta_scan(
   DeltaIn P{q, k, v, ld_qkv, beta, ld_beta, step, ld_step, step_bias, step_bias_dtype, rate_log, rate_log_dtype, state,
             state_stride, cu_q, state_slots, heads, kv_heads, dk, dv};
   HeadOut E{out, out_dtype, ldo, weight, weight_dtype, weight_stride, gate, ldg, eps, out_scale};
-#define LAUNCH(D)                                                                                              \
+#define LAUNCH_CP(D, WIDE)                                                                                     \
   {                                                                                                            \
-    constexpr int CT = chunk_tokens(D), SP = scan_split(D), CP = scan_columns(D), ROW = ScanShape<D, SP>::ROW;  \
+    constexpr int CT = chunk_tokens(D), SP = scan_split(D), CP = scan_columns(D, WIDE), ROW = ScanShape<D, SP>::ROW; \
     const int threads = ((dv + CP - 1) / CP * SP + 31) / 32 * 32, dvp = threads / SP * CP;                     \
     const size_t smem = ((size_t)3 * CT * ROW + (size_t)2 * CT * dvp + CT) * sizeof(float);                                                               \
     auto kern = gated_delta_scan_kernel<D, CT, SP, CP>;                                                                          \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
     co_launch_ex(true, kern, dim3(B, heads), dim3(threads), smem, stream, P, E);                               \
   }
+#define LAUNCH(D) if (dv * scan_split(D) > 128 * 16) LAUNCH_CP(D, true) else LAUNCH_CP(D, false)
   CO_SCAN_CASES(LAUNCH)
 #undef LAUNCH
+#undef LAUNCH_CP
   CO_CHECK_LAUNCH("gated_delta_scan");
   return 0;
 }
@@ -538,17 +567,19 @@ CO_EXPORT int coheryn_matrix_memory_scan(
   if (!(cap > 0.f)) CO_FAIL("matrix_memory_scan: the gate cap must be positive");
   MemoryIn P{q, k, v, ld, gi, gf, ld_gate, bias_i, bias_f, bias_dtype, cap, state, state_stride, cu_q, state_slots, heads, dk, dv};
   HeadOut E{out, out_dtype, ldo, weight, weight_dtype, weight_stride, gate, ldg, eps, out_scale};
-#define LAUNCH(D)                                                                                              \
+#define LAUNCH_CP(D, WIDE)                                                                                     \
   {                                                                                                            \
-    constexpr int CT = chunk_tokens(D), SP = scan_split(D), CP = scan_columns(D), ROW = ScanShape<D, SP>::ROW;  \
+    constexpr int CT = chunk_tokens(D), SP = scan_split(D), CP = scan_columns(D, WIDE), ROW = ScanShape<D, SP>::ROW; \
     const int threads = ((dv + CP - 1) / CP * SP + 31) / 32 * 32, dvp = threads / SP * CP;                     \
     const size_t smem = ((size_t)2 * CT * ROW + (size_t)2 * CT * dvp + 3 * CT) * sizeof(float);                                                               \
     auto kern = matrix_memory_scan_kernel<D, CT, SP, CP>;                                                                          \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
     co_launch_ex(true, kern, dim3(B, heads), dim3(threads), smem, stream, P, E);                               \
   }
+#define LAUNCH(D) if (dv * scan_split(D) > 128 * 16) LAUNCH_CP(D, true) else LAUNCH_CP(D, false)
   CO_SCAN_CASES(LAUNCH)
 #undef LAUNCH
+#undef LAUNCH_CP
   CO_CHECK_LAUNCH("matrix_memory_scan");
   return 0;
 }
