@@ -11,6 +11,20 @@ import math
 
 import numpy as np
 
+# ``forward(rounded=True)`` is the same model with what the bfloat16 engine hands from kernel to kernel in 16 bits
+# rounded to bfloat16 (the norm's output that every projection reads, queries, keys and values of the attention, the
+# activations in front of every output product) and nothing else changed: its distance from the unrounded model is
+# what eight bits of mantissa at those places cost this very row, the yardstick for the engine's bfloat16 rows.
+_ROUND = [False]
+
+
+def r16(x):
+    if not _ROUND[0]:
+        return x
+    bits = np.asarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    bits = (bits + 0x7FFF + ((bits >> 16) & 1)) & 0xFFFF0000
+    return bits.astype(np.uint32).view(np.float32).astype(np.float64)
+
 
 def rms(x, eps):
     return x / np.sqrt(np.mean(x * x, axis=-1, keepdims=True) + eps)
@@ -102,9 +116,9 @@ def left_attention(h, w, p, c, eps):
     q = rms(h @ w[p + ".q"].T, eps) * w[p + ".q.norm"]
     k = rms(h @ w[p + ".k"].T, eps) * w[p + ".k.norm"]
     v = h @ w[p + ".v"].T
-    o = biased_window_attention(q.reshape(T, H, dk), k.reshape(T, G, dk), v.reshape(T, G, dv), H, G,
+    o = biased_window_attention(r16(q).reshape(T, H, dk), r16(k).reshape(T, G, dk), r16(v).reshape(T, G, dv), H, G,
                                 c["scale"], c["mask"]["size"])
-    return o.reshape(T, H * dv) @ w[p + ".o"].T
+    return r16(o.reshape(T, H * dv)) @ w[p + ".o"].T
 
 
 def right_delta(h, w, p, c, eps):
@@ -124,7 +138,7 @@ def right_delta(h, w, p, c, eps):
     o = np.stack([gated_delta_rule(q[:, x // per], k[:, x // per], v[:, x], beta[:, x], decay[:, x])
                   for x in range(H)], axis=1)                                    # [T, H, dv]
     o = rms(o, eps) * w[p + ".norm"] * gate
-    return o.reshape(T, H * dv) @ w[p + ".o"].T
+    return r16(o.reshape(T, H * dv)) @ w[p + ".o"].T
 
 
 def side_by_side(h, w, p, c, eps):
@@ -142,11 +156,11 @@ def mlstm(h, w, p, c, eps):
     log_f = log_sigmoid(cap * np.tanh((h @ w[p + ".f"].T + w[p + ".f.b"]) / cap))
     o = np.stack([matrix_memory(q[:, x], k[:, x], v[:, x], log_i[:, x], log_f[:, x]) for x in range(H)], axis=1)
     o = rms(o, eps).reshape(T, H * dv) * w[p + ".norm"] * sigmoid(h @ w[p + ".g"].T)
-    return o @ w[p + ".o"].T
+    return r16(o) @ w[p + ".o"].T
 
 
 def dense_ff(h, w, p):
-    return (gelu_tanh(h @ w[p + ".gate"].T) * (h @ w[p + ".up"].T)) @ w[p + ".down"].T
+    return r16(gelu_tanh(h @ w[p + ".gate"].T) * (h @ w[p + ".up"].T)) @ w[p + ".down"].T
 
 
 MIXERS = {"parallel": side_by_side, "mlstm": mlstm}
@@ -166,9 +180,17 @@ def layer_order(config):
     return runs + [(i, None) for i in range(b, n)]
 
 
-def forward(config, w, tokens, layer_outputs=None):
+def forward(config, w, tokens, layer_outputs=None, rounded=False):
     """Logits [T, vocab] of one whole sequence; ``layer_outputs`` (a list) receives the stream after
-    every layer run."""
+    every layer run; ``rounded``: see ``r16``."""
+    _ROUND[0] = bool(rounded)
+    try:
+        return _forward(config, w, tokens, layer_outputs)
+    finally:
+        _ROUND[0] = False
+
+
+def _forward(config, w, tokens, layer_outputs):
     w = {k: np.asarray(v, dtype=np.float64) for k, v in w.items()}
     eps = config["norm"]["eps"]
     x0 = w["embed"][np.asarray(tokens)] * config["embedding"]["scale"]
@@ -180,13 +202,13 @@ def forward(config, w, tokens, layer_outputs=None):
             x = x + w["loop.step"][opens]
         L = config["layers"][i]
         p = f"l{i}"
-        h = rms(x, eps) * w[p + ".norm1"]
+        h = r16(rms(x, eps) * w[p + ".norm1"])
         y = MIXERS[L["type"]](h, w, p + ".mix", L["mixer"], eps)
         if L.get("mlp") is not None:
             y = y + dense_ff(h, w, p + ".mlp")
         x = x + y
         if layer_outputs is not None:
             layer_outputs.append(x.copy())
-    z = (rms(x, eps) * w["final.norm"]) @ w["head"].T * config["logit_scale"]
+    z = r16(rms(x, eps) * w["final.norm"]) @ w["head"].T * config["logit_scale"]
     cap = config["logit_softcap"]
     return cap * np.tanh(z / cap)

@@ -112,3 +112,24 @@ def test_random_weights_need_the_inner_sizes(tmp_path):
     d = kc.make_folder(tmp_path, "K3")
     config, w = kc.read_model(d)
     assert w["l1.mix.right.a1"].shape == (16, 64) and config["layers"][1]["mixer"]["right"]["conv"] == 1
+
+
+def test_the_bfloat16_bound_sees_one_wrong_token(tmp_path):
+    """On the plain model: ONE other token two or five places back (one wrong key, value and state update in every
+    layer) moves the last row by more than one and a half bounds, so the bound the bfloat16 rows are held to cannot
+    swallow such a fault.  (These random models forget within some tens of tokens: their decays are far from one.  What a
+    token FAR back is worth is tested on the kernels, with gates and keys made to stand out.)"""
+    import numpy as np
+    from replay import bf16_excess
+    for name in ("K1", "K2", "K3"):
+        folder = kc.make_folder(tmp_path, name)
+        vocab = kc.CASES[name][0]["vocab"]
+        seq = kc.prompt(90, 48, vocab)
+        ref = kc.plain_rows(folder, seq)[-1].astype(np.float32)
+        twin = kc.plain_rows(folder, seq, rounded=True)[-1].astype(np.float32)
+        assert bf16_excess(twin, ref, twin) <= 1.0
+        for place in (46, 43):
+            other = list(seq)
+            other[place] = (other[place] + 1) % vocab
+            moved = kc.plain_rows(folder, other)[-1].astype(np.float32)
+            assert bf16_excess(moved, ref, twin) > 1.5, (name, place, bf16_excess(moved, ref, twin))
