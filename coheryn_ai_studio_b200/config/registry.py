@@ -83,7 +83,7 @@ class Architecture:
         for ts in specs.values():
             count = 1
             for d in ts.shape:
-                count *= int(d)
+                count *= max(int(d), 0)      # a size that only the checkpoint gives counts as unknown
             parameters += count
         caps = Capabilities(
             adapter=self.adapter_id or f"{self.name.lower()}-b200-v1", architecture=self.name,

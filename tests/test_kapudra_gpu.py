@@ -430,5 +430,35 @@ def test_trace_program_replays_a_schedule(folders, tmp_path):
     kc.check_rows(rows, folders[name], {"a": a, "b": b}, "float32", "trace")
 
 
+def test_command_line_runs_and_traces_the_design(folders):
+    """`coheryn run` (greedy tokens) and `coheryn trace` (every layer run's output and the logits per position) on a folder
+    of this design, and the Python entry point, against the plain implementation."""
+    import json, os, subprocess, sys
+    from coheryn_ai_studio_b200 import api
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    name = "K1"
+    p = kc.prompt(85, 7, vocab(name))
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "coheryn"), "run", folders[name], "--tokens", ",".join(map(str, p)),
+                        "--max-tokens", "5", "--context", "64", "--dtype", "float32", "--stream"], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = [int(t) for t in r.stdout.split()]
+    ids = list(p)
+    for tok in got:
+        assert tok == int(np.argmax(kc.plain_rows(folders[name], ids)[-1]))
+        ids.append(tok)
+    assert api.generate(folders[name], [p], max_tokens=5, context=64, dtype="float32")[0]["token_ids"] == got
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "coheryn"), "trace", folders[name], "--tokens", ",".join(map(str, p)),
+                        "--context", "64", "--dtype", "float32"], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    config, w = kc.read_model(folders[name])
+    layers = []
+    ref = plain.forward(config, w, p, layers)
+    assert len(lines) == len(p) * (len(layers) + 1)
+    for l in lines:
+        want = ref[l["position"]] if l["name"] == "logits" else layers[int(l["name"].split(".")[1])][l["position"]]
+        assert np.abs(np.asarray(l["values"], np.float64) - want).max() <= 2e-4 * max(1.0, float(np.abs(want).max())), l["name"]
+
+
 def test_zz_report():
     print(f"\nlargest float32 difference {kc.WORST['float32']:.2e}; bfloat16 rows reached {kc.WORST['bfloat16']:.2f} of their bound")
