@@ -90,6 +90,12 @@ struct HeadOut {
   int weight_stride;
   const float* gate; long ldg;                 // pre-activations [T, heads * dv]
   float eps, out_scale;
+  // When the columns of a head are split over several CTAs (a long prompt of few requests: more SMs at work), no CTA sees a
+  // whole head: the scans then leave the unnormalised outputs in `raw` [T, heads * dv] and a second kernel applies norm,
+  // weight and gate, in the same order of operations.  `nm_next`: where the matrix memory's n and m of each (request,
+  // head) wait until every CTA of the head has read the old ones ([B][heads][dk + 1]).
+  float* raw; long ldr;
+  float* nm_next;
 };
 
 __device__ __forceinline__ void head_out_chunk(const HeadOut& E, const float* os, int dvp, int dv, int nt, int row0, int h) {
@@ -107,6 +113,42 @@ __device__ __forceinline__ void head_out_chunk(const HeadOut& E, const float* os
       rc_store(E.out, E.out_dtype, row * E.ldo + (size_t)h * dv + c, os[i * dvp + c] * inv * w * g * E.out_scale);
     }
   }
+}
+
+// The unnormalised outputs of a chunk for the CTA's columns (see HeadOut::raw).
+__device__ __forceinline__ void raw_out_chunk(const HeadOut& E, const float* os, int dvp, int dv, int colbase, int nt, int row0, int h) {
+  for (int e = threadIdx.x; e < nt * dvp; e += blockDim.x) {
+    const int i = e / dvp, c = e % dvp;
+    if (colbase + c < dv) E.raw[(size_t)(row0 + i) * E.ldr + (size_t)h * dv + colbase + c] = os[e];
+  }
+}
+
+// Norm, weight and gate of whole heads from the unnormalised outputs: 16 tokens of a head per CTA, through the same
+// function and therefore the same order of operations as the scans' own epilogue.
+__global__ void __launch_bounds__(256) head_norm_gate_kernel(HeadOut E, int T, int dv) {
+  extern __shared__ __align__(16) float smem[];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int row0 = blockIdx.x * 16, h = blockIdx.y, nt = min(16, T - row0);
+  for (int e = threadIdx.x; e < nt * dv; e += blockDim.x) {
+    const int i = e / dv, c = e % dv;
+    smem[e] = E.raw[(size_t)(row0 + i) * E.ldr + (size_t)h * dv + c];
+  }
+  __syncthreads();
+  head_out_chunk(E, smem, dv, dv, nt, row0, h);
+}
+
+// n and m of the matrix memory from the side into the state (see HeadOut::nm_next).
+__global__ void memory_nm_commit_kernel(const float* __restrict__ nm, float* __restrict__ state, long state_stride,
+                                        const int* __restrict__ state_slots, const int* __restrict__ cu_q, int heads, int dk, int dv) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int r = blockIdx.x, h = blockIdx.y;
+  if (cu_q[r + 1] - cu_q[r] <= 0) return;
+  float* slot = state + (size_t)state_slots[r] * state_stride;
+  const float* from = nm + ((size_t)r * heads + h) * (dk + 1);
+  for (int d = threadIdx.x; d < dk; d += blockDim.x) slot[(size_t)heads * dk * dv + (size_t)h * dk + d] = from[d];
+  if (threadIdx.x == 0) slot[(size_t)heads * dk * dv + (size_t)heads * dk + h] = from[dk];
 }
 
 // ---------------------------------------------------------------------------------
@@ -200,6 +242,7 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(DeltaIn P, HeadOu
   const int r = blockIdx.x, h = blockIdx.y;
   const int part = threadIdx.x % SPLIT, col0 = (threadIdx.x / SPLIT) * CP, d0 = part * DP;
   const int dk = P.dk, dv = P.dv, dvp = (blockDim.x / SPLIT) * CP;
+  const int colbase = blockIdx.z * dvp;        // this CTA's first column of the head
   const int start = P.cu_q[r], len = P.cu_q[r + 1] - start;
   if (len <= 0) return;
   const int g = h / (P.heads / P.kv_heads);
@@ -211,7 +254,7 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(DeltaIn P, HeadOu
   float* betas = os + CT * dvp;        // [CT]
   float* S_state = P.state + (size_t)P.state_slots[r] * P.state_stride + (size_t)h * dk * dv;
   float S[CP][DP];
-  scan_state_load<CP, DP>(S, S_state, d0, col0, dk, dv);
+  scan_state_load<CP, DP>(S, S_state, d0, colbase + col0, dk, dv);
   const float rate = expf(co_load_any(P.rate_log, P.rate_log_dtype, h));
   const float q_scale = 1.0f / sqrtf((float)dk);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -235,7 +278,7 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(DeltaIn P, HeadOu
 #pragma unroll 8
     for (int e = threadIdx.x; e < nt * dvp; e += blockDim.x) {
       const int i = e / dvp, c = e % dvp;
-      vs[e] = c < dv ? P.v[(size_t)(row0 + i) * P.ld_qkv + (size_t)h * dv + c] : 0.f;
+      vs[e] = colbase + c < dv ? P.v[(size_t)(row0 + i) * P.ld_qkv + (size_t)h * dv + colbase + c] : 0.f;
     }
     if (threadIdx.x < nt) betas[threadIdx.x] = rc_sigmoid(P.beta[(size_t)(row0 + threadIdx.x) * P.ld_beta + h]);
     __syncthreads();
@@ -299,10 +342,11 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(DeltaIn P, HeadOu
       for (int d = 0; d < DP / 4; ++d) { kc[d] = kn[d]; gc[d] = gn[d]; qc[d] = qn[d]; }
     }
     __syncthreads();
-    head_out_chunk(E, os, dvp, dv, nt, row0, h);
+    if (E.raw) raw_out_chunk(E, os, dvp, dv, colbase, nt, row0, h);
+    else head_out_chunk(E, os, dvp, dv, nt, row0, h);
     __syncthreads();
   }
-  scan_state_store<CP, DP>(S, S_state, d0, col0, dk, dv);
+  scan_state_store<CP, DP>(S, S_state, d0, colbase + col0, dk, dv);
 }
 
 // ---------------------------------------------------------------------------------
@@ -328,6 +372,7 @@ __global__ void __launch_bounds__(512) matrix_memory_scan_kernel(MemoryIn P, Hea
   const int r = blockIdx.x, h = blockIdx.y;
   const int part = threadIdx.x % SPLIT, col0 = (threadIdx.x / SPLIT) * CP, d0 = part * DP;
   const int dk = P.dk, dv = P.dv, dvp = (blockDim.x / SPLIT) * CP;
+  const int colbase = blockIdx.z * dvp;        // this CTA's first column of the head
   const int start = P.cu_q[r], len = P.cu_q[r + 1] - start;
   if (len <= 0) return;
   float* qs = smem;                    // [CT][ROW]
@@ -342,7 +387,7 @@ __global__ void __launch_bounds__(512) matrix_memory_scan_kernel(MemoryIn P, Hea
   float* n_state = slot + (size_t)P.heads * dk * dv + (size_t)h * dk;
   float* m_state = slot + (size_t)P.heads * dk * dv + (size_t)P.heads * dk + h;
   float S[CP][DP];
-  scan_state_load<CP, DP>(S, S_state, d0, col0, dk, dv);
+  scan_state_load<CP, DP>(S, S_state, d0, colbase + col0, dk, dv);
   constexpr int NJ = (DK + 31) / 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   float nreg[NJ];                      // warp 0: lane holds n[lane + 32 j]
@@ -368,7 +413,7 @@ __global__ void __launch_bounds__(512) matrix_memory_scan_kernel(MemoryIn P, Hea
 #pragma unroll 8
     for (int e = threadIdx.x; e < nt * dvp; e += blockDim.x) {
       const int i = e / dvp, c = e % dvp;
-      vs[e] = c < dv ? P.v[(size_t)(row0 + i) * P.ld + (size_t)h * dv + c] : 0.f;
+      vs[e] = colbase + c < dv ? P.v[(size_t)(row0 + i) * P.ld + (size_t)h * dv + colbase + c] : 0.f;
     }
     if (threadIdx.x < nt) {
       const size_t row = (size_t)(row0 + threadIdx.x);
@@ -430,15 +475,19 @@ __global__ void __launch_bounds__(512) matrix_memory_scan_kernel(MemoryIn P, Hea
       for (int d = 0; d < DP / 4; ++d) { kc[d] = kn[d]; qc[d] = qn[d]; }
     }
     __syncthreads();
-    head_out_chunk(E, os, dvp, dv, nt, row0, h);
+    if (E.raw) raw_out_chunk(E, os, dvp, dv, colbase, nt, row0, h);
+    else head_out_chunk(E, os, dvp, dv, nt, row0, h);
     __syncthreads();
   }
-  scan_state_store<CP, DP>(S, S_state, d0, col0, dk, dv);
-  if (warp == 0) {
+  scan_state_store<CP, DP>(S, S_state, d0, colbase + col0, dk, dv);
+  if (warp == 0 && blockIdx.z == 0) {
+    // with the head's columns split over CTAs the others may not have read n and m yet: they go to the side
+    float* n_to = E.nm_next ? E.nm_next + ((size_t)r * P.heads + h) * (dk + 1) : n_state;
+    float* m_to = E.nm_next ? n_to + dk : m_state;
 #pragma unroll
     for (int j = 0; j < NJ; ++j)
-      if (lane + 32 * j < dk) n_state[lane + 32 * j] = nreg[j];
-    if (lane == 0) *m_state = m;
+      if (lane + 32 * j < dk) n_to[lane + 32 * j] = nreg[j];
+    if (lane == 0) *m_to = m;
   }
 }
 
@@ -520,6 +569,24 @@ CO_EXPORT int coheryn_short_conv_silu(const float* x, long ldx, float* y, long l
   else if (dk <= 64) { LAUNCH(64) } else if (dk <= 96) { LAUNCH(96) } else if (dk <= 128) { LAUNCH(128) } \
   else if (dk <= 192) { LAUNCH(192) } else { LAUNCH(256) }
 
+// Into how many CTAs the columns of a head are split: one (the scan's own epilogue normalises whole heads) unless the
+// step is a long prompt of few requests, where a CTA per head would leave most SMs idle; then 64 columns per CTA, the
+// unnormalised outputs in the caller's scratch (total_tokens * heads * dv floats, then `extra`) and the norm in a kernel
+// of its own.  A column's arithmetic is the same either way.
+constexpr int SLICE_COLUMNS = 64;
+static int scan_slices(int B, int heads, int dv, int total_tokens, const float* scratch, long scratch_floats, long extra) {
+  if (!scratch || dv <= SLICE_COLUMNS || (long)B * heads > 74 || total_tokens < 64 * B) return 1;
+  if (scratch_floats < (long)total_tokens * heads * dv + extra) return 1;
+  return (dv + SLICE_COLUMNS - 1) / SLICE_COLUMNS;
+}
+
+static int launch_head_norm_gate(const HeadOut& E, int T, int heads, int dv, cudaStream_t stream) {
+  const size_t smem = (size_t)16 * dv * sizeof(float);
+  co_launch(head_norm_gate_kernel, dim3((T + 15) / 16, heads), dim3(256), smem, stream, E, T, dv);
+  CO_CHECK_LAUNCH("head_norm_gate");
+  return 0;
+}
+
 static int scan_shape_ok(const char* name, int heads, int dk, int dv) {
   if (heads < 1 || dk < 1 || dk > 256 || dv < 1 || dv > 256) {
     co_set_error("%s: heads %d, key channels %d (1..256), value channels %d (1..256)", name, heads, dk, dv);
@@ -533,55 +600,66 @@ CO_EXPORT int coheryn_gated_delta_scan(
     long ld_step, const void* step_bias, int step_bias_dtype, const void* rate_log, int rate_log_dtype, float* state,
     long state_stride, const int* cu_q, const int* state_slots, int B, int heads, int kv_heads, int dk, int dv, void* out,
     int out_dtype, long ldo, const void* weight, int weight_dtype, int weight_stride, const float* gate, long ldg, float eps,
-    float out_scale, cudaStream_t stream) {
+    float out_scale, int total_tokens, float* scratch, long scratch_floats, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (!scan_shape_ok("gated_delta_scan", heads, dk, dv)) return 1;
+  const int slices = scan_slices(B, heads, dv, total_tokens, scratch, scratch_floats, 0);
   if (kv_heads < 1 || heads % kv_heads) CO_FAIL("gated_delta_scan: %d heads do not group over %d q/k heads", heads, kv_heads);
   DeltaIn P{q, k, v, ld_qkv, beta, ld_beta, step, ld_step, step_bias, step_bias_dtype, rate_log, rate_log_dtype, state,
             state_stride, cu_q, state_slots, heads, kv_heads, dk, dv};
-  HeadOut E{out, out_dtype, ldo, weight, weight_dtype, weight_stride, gate, ldg, eps, out_scale};
+  HeadOut E{out, out_dtype, ldo, weight, weight_dtype, weight_stride, gate, ldg, eps, out_scale,
+            slices > 1 ? scratch : nullptr, (long)heads * dv, nullptr};
 #define LAUNCH_CP(D, WIDE)                                                                                     \
   {                                                                                                            \
     constexpr int CT = chunk_tokens(D), SP = scan_split(D), CP = scan_columns(D, WIDE), ROW = ScanShape<D, SP>::ROW; \
-    const int threads = ((dv + CP - 1) / CP * SP + 31) / 32 * 32, dvp = threads / SP * CP;                     \
+    const int cols = slices > 1 ? SLICE_COLUMNS : dv;                                                                     \
+    const int threads = ((cols + CP - 1) / CP * SP + 31) / 32 * 32, dvp = threads / SP * CP;                   \
     const size_t smem = ((size_t)3 * CT * ROW + (size_t)2 * CT * dvp + CT) * sizeof(float);                                                               \
     auto kern = gated_delta_scan_kernel<D, CT, SP, CP>;                                                                          \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-    co_launch_ex(true, kern, dim3(B, heads), dim3(threads), smem, stream, P, E);                               \
+    co_launch_ex(true, kern, dim3(B, heads, slices > 1 ? (dv + dvp - 1) / dvp : 1), dim3(threads), smem, stream, P, E); \
   }
-#define LAUNCH(D) if (dv * scan_split(D) > 128 * 16) LAUNCH_CP(D, true) else LAUNCH_CP(D, false)
+#define LAUNCH(D) if (slices == 1 && dv * scan_split(D) > 128 * 16) LAUNCH_CP(D, true) else LAUNCH_CP(D, false)
   CO_SCAN_CASES(LAUNCH)
 #undef LAUNCH
 #undef LAUNCH_CP
   CO_CHECK_LAUNCH("gated_delta_scan");
-  return 0;
+  return slices > 1 ? launch_head_norm_gate(E, total_tokens, heads, dv, stream) : 0;
 }
 
 CO_EXPORT int coheryn_matrix_memory_scan(
     const float* q, const float* k, const float* v, long ld, const float* gi, const float* gf, long ld_gate,
     const void* bias_i, const void* bias_f, int bias_dtype, float cap, float* state, long state_stride, const int* cu_q,
     const int* state_slots, int B, int heads, int dk, int dv, void* out, int out_dtype, long ldo, const void* weight,
-    int weight_dtype, int weight_stride, const float* gate, long ldg, float eps, float out_scale, cudaStream_t stream) {
+    int weight_dtype, int weight_stride, const float* gate, long ldg, float eps, float out_scale, int total_tokens,
+    float* scratch, long scratch_floats, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (!scan_shape_ok("matrix_memory_scan", heads, dk, dv)) return 1;
+  const int slices = scan_slices(B, heads, dv, total_tokens, scratch, scratch_floats, (long)B * heads * (dk + 1));
   if (!(cap > 0.f)) CO_FAIL("matrix_memory_scan: the gate cap must be positive");
   MemoryIn P{q, k, v, ld, gi, gf, ld_gate, bias_i, bias_f, bias_dtype, cap, state, state_stride, cu_q, state_slots, heads, dk, dv};
-  HeadOut E{out, out_dtype, ldo, weight, weight_dtype, weight_stride, gate, ldg, eps, out_scale};
+  HeadOut E{out, out_dtype, ldo, weight, weight_dtype, weight_stride, gate, ldg, eps, out_scale,
+            slices > 1 ? scratch : nullptr, (long)heads * dv, slices > 1 ? scratch + (long)total_tokens * heads * dv : nullptr};
 #define LAUNCH_CP(D, WIDE)                                                                                     \
   {                                                                                                            \
     constexpr int CT = chunk_tokens(D), SP = scan_split(D), CP = scan_columns(D, WIDE), ROW = ScanShape<D, SP>::ROW; \
-    const int threads = ((dv + CP - 1) / CP * SP + 31) / 32 * 32, dvp = threads / SP * CP;                     \
+    const int cols = slices > 1 ? SLICE_COLUMNS : dv;                                                                     \
+    const int threads = ((cols + CP - 1) / CP * SP + 31) / 32 * 32, dvp = threads / SP * CP;                   \
     const size_t smem = ((size_t)2 * CT * ROW + (size_t)2 * CT * dvp + 3 * CT) * sizeof(float);                                                               \
     auto kern = matrix_memory_scan_kernel<D, CT, SP, CP>;                                                                          \
     if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-    co_launch_ex(true, kern, dim3(B, heads), dim3(threads), smem, stream, P, E);                               \
+    co_launch_ex(true, kern, dim3(B, heads, slices > 1 ? (dv + dvp - 1) / dvp : 1), dim3(threads), smem, stream, P, E); \
   }
-#define LAUNCH(D) if (dv * scan_split(D) > 128 * 16) LAUNCH_CP(D, true) else LAUNCH_CP(D, false)
+#define LAUNCH(D) if (slices == 1 && dv * scan_split(D) > 128 * 16) LAUNCH_CP(D, true) else LAUNCH_CP(D, false)
   CO_SCAN_CASES(LAUNCH)
 #undef LAUNCH
 #undef LAUNCH_CP
   CO_CHECK_LAUNCH("matrix_memory_scan");
-  return 0;
+  if (slices == 1) return 0;
+  co_launch(memory_nm_commit_kernel, dim3(B, heads), dim3(128), 0, stream, (const float*)E.nm_next, state, state_stride, state_slots,
+            cu_q, heads, dk, dv);
+  CO_CHECK_LAUNCH("memory_nm_commit");
+  return launch_head_norm_gate(E, total_tokens, heads, dv, stream);
 }
 
 CO_EXPORT int coheryn_qk_norm_kv_write(const float* q, const float* k, const float* v, long ld, const void* wq, const void* wk,

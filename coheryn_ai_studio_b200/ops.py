@@ -914,6 +914,14 @@ def _f32(t: torch.Tensor, name: str) -> None:
         raise KernelError(f"{name} must be float32 with contiguous rows")
 
 
+def _scan_scratch(T: int, B: int, heads: int, dv: int, extra: int, device):
+    """Scratch for a scan that may split the columns of its heads over several CTAs (a long prompt of few requests; the
+    library decides by the same numbers): the unnormalised outputs, then ``extra`` floats.  None when it will not."""
+    if dv <= 64 or B * heads > 74 or T < 64 * B:
+        return None
+    return torch.empty(T * heads * dv + extra, dtype=torch.float32, device=device)
+
+
 def short_conv_silu(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, step, update_state: bool = True) -> torch.Tensor:
     """y[t, c] = silu(sum_j taps[c, j] * x[t - (n-1) + j, c]) over each request's run of tokens; inputs before the
     step's first token come from ``state`` (a float32 view [slots, (n-1) * C] whose rows may be strided), which then
@@ -947,13 +955,14 @@ def gated_delta_scan(q, k, v, beta, step_pre, step_bias, rate_log, state, step, 
     assert step_bias.numel() == heads * dk and rate_log.numel() == heads and norm_weight.numel() == dv
     assert state.shape[1] == heads * dk * dv and out.shape == (q.shape[0], heads * dv) and out.stride(1) == 1
     lib = recurrent()
+    scratch = _scan_scratch(q.shape[0], step.num_requests, heads, dv, 0, q.device)
     _check(lib, lib.coheryn_gated_delta_scan(
         _ptr(q), _ptr(k), _ptr(v), c_long(q.stride(0)), _ptr(beta), c_long(beta.stride(0)), _ptr(step_pre),
         c_long(step_pre.stride(0)), _ptr(step_bias), c_int(_code(step_bias)), _ptr(rate_log), c_int(_code(rate_log)),
         _ptr(state), c_long(state.stride(0)), _ptr(step.cu_q), _ptr(step.state_slots), c_int(step.num_requests),
         c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv), _ptr(out), c_int(_code(out)), c_long(out.stride(0)),
         _ptr(norm_weight), c_int(_code(norm_weight)), c_int(0), _ptr(gate), c_long(gate.stride(0)), c_float(eps),
-        c_float(out_scale), _stream()))
+        c_float(out_scale), c_int(q.shape[0]), _ptr(scratch), c_long(scratch.numel() if scratch is not None else 0), _stream()))
 
 
 def matrix_memory_scan(q, k, v, gate_i, gate_f, bias_i, bias_f, cap: float, state, step, heads: int, dk: int, dv: int,
@@ -972,12 +981,14 @@ def matrix_memory_scan(q, k, v, gate_i, gate_f, bias_i, bias_f, cap: float, stat
     assert norm_weight.numel() == heads * dv
     assert state.shape[1] == heads * (dk * dv + dk + 1) and out.shape == (q.shape[0], heads * dv) and out.stride(1) == 1
     lib = recurrent()
+    scratch = _scan_scratch(q.shape[0], step.num_requests, heads, dv, step.num_requests * heads * (dk + 1), q.device)
     _check(lib, lib.coheryn_matrix_memory_scan(
         _ptr(q), _ptr(k), _ptr(v), c_long(q.stride(0)), _ptr(gate_i), _ptr(gate_f), c_long(gate_i.stride(0)), _ptr(bias_i),
         _ptr(bias_f), c_int(_code(bias_i)), c_float(cap), _ptr(state), c_long(state.stride(0)), _ptr(step.cu_q),
         _ptr(step.state_slots), c_int(step.num_requests), c_int(heads), c_int(dk), c_int(dv), _ptr(out), c_int(_code(out)),
         c_long(out.stride(0)), _ptr(norm_weight), c_int(_code(norm_weight)), c_int(dv), _ptr(gate), c_long(gate.stride(0)),
-        c_float(eps), c_float(out_scale), _stream()))
+        c_float(eps), c_float(out_scale), c_int(q.shape[0]), _ptr(scratch), c_long(scratch.numel() if scratch is not None else 0),
+        _stream()))
 
 
 def qk_norm_kv_write(q, k, v, q_weight, k_weight, eps: float, slots, k_cache, v_cache, num_heads: int, num_kv_heads: int,
