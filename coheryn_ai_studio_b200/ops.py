@@ -816,6 +816,16 @@ ATTN_OPROJ_MERGE_BYTES = int(os.environ.get("COHERYN_ATTN_OPROJ_BYTES", str(32 <
 NATIVE_BLOCK = os.environ.get("COHERYN_NATIVE_BLOCK", "1") != "0"
 
 
+# Whether a block whose producers can hand over their activations multiplies them by the stacked output matrices in
+# ONE product (parts/block.py: ParallelResidual) instead of one product per producer.
+JOINED_OUTPUT = os.environ.get("COHERYN_JOINED_OUTPUT", "1") != "0"
+
+
+def set_joined_output(on: bool) -> None:
+    global JOINED_OUTPUT
+    JOINED_OUTPUT = bool(on)
+
+
 def set_native_block(on: bool) -> None:
     global NATIVE_BLOCK
     NATIVE_BLOCK = bool(on)
@@ -872,13 +882,18 @@ def gated_activation_code(activation: str) -> int:
                           f"(built: {', '.join(sorted(GATED_ACTIVATIONS))})") from None
 
 
-def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, activation: str = "silu",
+                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """act(x @ Wg.T) * (x @ Wu.T) for w_gate_up with INTERLEAVED rows (row 2j = gate_j,
-    row 2j+1 = up_j), so that a gate/up pair lands in one thread of the epilogue."""
+    row 2j+1 = up_j), so that a gate/up pair lands in one thread of the epilogue.  ``out`` ([M, I] of x's dtype, rows
+    may be strided: a column slice of a wider buffer) receives the result when given."""
     code = gated_activation_code(activation)
     M = x.shape[0]
     I = w_gate_up.shape[0] // 2
-    out = torch.empty((M, I), dtype=x.dtype, device=x.device)
+    if out is None:
+        out = torch.empty((M, I), dtype=x.dtype, device=x.device)
+    else:
+        assert out.shape == (M, I) and out.dtype == x.dtype and out.stride(1) == 1
     if M == 0:
         return out
     if _few_ok(x, w_gate_up):
@@ -892,7 +907,12 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, activation: str = "si
         return out
     gu = torch.empty((M, 2 * I), dtype=x.dtype, device=x.device)
     gemm_simt(x, w_gate_up, None, gu)
-    silu_mul(gu, out, code)
+    if out.is_contiguous():
+        silu_mul(gu, out, code)
+    else:
+        tmp = torch.empty((M, I), dtype=x.dtype, device=x.device)
+        silu_mul(gu, tmp, code)
+        out.copy_(tmp)
     return out
 
 

@@ -184,7 +184,16 @@ class DistanceBiasAttention(Mixer):
             self.slopes = slopes.to(torch.float32).to(self.w_o.device)
             self.slopes_log2 = (slopes * ops.LOG2_E).to(torch.float32).to(self.w_o.device)
 
+    def output_weights(self):
+        return [self.w_o]
+
     def forward_into(self, x: torch.Tensor, step: StepContext, cache: LayerCache, out: torch.Tensor) -> None:
+        o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
+        self.forward_open(x, step, cache, [o])
+        ops.linear(o, self.w_o, out=out[0])
+
+    def forward_open(self, x: torch.Tensor, step: StepContext, cache: LayerCache, outs) -> None:
+        """The attention's output in front of the output product into ``outs[0]`` ([T, heads * dv], rows may be strided)."""
         Attention._check(cache)
         H, G, dk, dv = self.num_heads, self.num_kv_heads, self.dk, self.dv
         nq, nk = H * dk, G * dk
@@ -201,10 +210,8 @@ class DistanceBiasAttention(Mixer):
         q = ops.qk_norm_kv_write(proj[:, :nq], proj[:, nq:nq + nk], proj[:, nq + nk:], self.q_norm, self.k_norm, self.eps,
                                  slots, cache.k, cache.v, H, G, dk, dv, cache.page_size, self.runtime.dtype,
                                  v_scale=self.out_scale)      # the output's constant rides on the values
-        o = torch.empty((x.shape[0], H * dv), dtype=self.runtime.dtype, device=x.device)
-        ops.attention_biased(q, o, cache.k, cache.v, step, cache.group, H, G, dk, dv, cache.page_size, self.window,
+        ops.attention_biased(q, outs[0], cache.k, cache.v, step, cache.group, H, G, dk, dv, cache.page_size, self.window,
                              self.scale, self.slopes, self.slopes_log2)
-        ops.linear(o, self.w_o, out=out[0])
 
     def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
         out = torch.empty((1, x.shape[0], self.hidden_size), dtype=torch.float32, device=x.device)

@@ -75,10 +75,43 @@ class ParallelResidual(Arrangement):
         names = self.names or self.NAMES
         return {names[slot]: part for slot, part in self.slots.items()}
 
+    _joined = None     # None: not looked at yet; False: the producers write their own summands
+
+    def _joined_output(self):
+        """[o_1 | o_2 | ..] times the output matrices stacked side by side is the sum of the producers' outputs: ONE
+        product instead of one per producer, when every producer hands its activations over and every piece starts on
+        a 16-byte boundary in bfloat16 (eight elements).  Returns (stacked matrix, column ranges) or False."""
+        if self._joined is None:
+            self._joined = False
+            producers = self.producers()
+            if all(hasattr(p, "forward_open") and hasattr(p, "output_weights") for p in producers):
+                weights = [p.output_weights() for p in producers]
+                if all(w is not None for w in weights):
+                    flat = [w for ws in weights for w in ws]
+                    if all(w.dim() == 2 and w.shape[1] % 8 == 0 and w.dtype == flat[0].dtype for w in flat):
+                        ranges, at = [], 0
+                        for w in flat:
+                            ranges.append((at, at + w.shape[1]))
+                            at += w.shape[1]
+                        self._joined = (torch.cat(flat, dim=1).contiguous(), ranges, [len(ws) for ws in weights])
+        return self._joined
+
     def forward(self, residual, delta, step, cache):
         if not self.mixer.partial_output:
             raise ValueError("parallel_residual needs a model whose norms all take partial sums")
         h = self.norm.forward(residual, delta)
+        joined = self._joined_output() if ops.JOINED_OUTPUT else False
+        if joined:
+            w_out, ranges, counts = joined
+            T = residual.shape[0]
+            acts = torch.empty((T, w_out.shape[1]), dtype=w_out.dtype, device=residual.device)
+            views = [acts[:, a:b] for a, b in ranges]
+            self.mixer.forward_open(h, step, cache, views[:counts[0]])
+            if self.feed_forward is not None:
+                self.feed_forward.forward_open(h, step, None, views[counts[0]:])
+            # a long K: the product may leave its K slices to the next norm (a float32 stack), as the down projection does
+            out = ops.linear(acts, w_out, out_dtype=torch.float32, partial_ok=True)
+            return residual, out if out.dim() == 3 else out.unsqueeze(0)
         n_mix = self.mixer.output_parts
         n = n_mix + (self.feed_forward.output_parts if self.feed_forward is not None else 0)
         out = torch.empty((n, residual.shape[0], residual.shape[1]), dtype=torch.float32, device=residual.device)

@@ -42,6 +42,14 @@ class GatedMLP(FeedForward):
 
     output_parts = 1
 
+    # A block may take the output product over: it concatenates the activations of all its producers and multiplies them
+    # by their stacked output matrices once (see ParallelResidual).
+    def output_weights(self):
+        return [self.w_down]
+
+    def forward_open(self, x: torch.Tensor, step: StepContext, cache, outs) -> None:
+        ops.gated_linear(x, self.w_gate_up, self.activation, out=outs[0])
+
     def forward_into(self, x: torch.Tensor, step: StepContext, out: torch.Tensor) -> None:
         """The output written into ``out`` (float32 [1, T, H]): one of the summands that a block hands to the next norm."""
         ops.linear(ops.gated_linear(x, self.w_gate_up, self.activation), self.w_down, out=out[0])

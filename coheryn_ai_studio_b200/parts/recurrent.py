@@ -96,14 +96,22 @@ class MatrixMemory(_StateMixer):
         dt = torch.float32 if torch.float32 in (tensors["i.b"].dtype, tensors["f.b"].dtype) else tensors["i.b"].dtype
         self.b_i, self.b_f = tensors["i.b"].to(dt).contiguous(), tensors["f.b"].to(dt).contiguous()
 
+    def output_weights(self):
+        return [self.w_o]
+
     def forward_into(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], out: torch.Tensor) -> None:
+        o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
+        self.forward_open(x, step, cache, [o])
+        ops.linear(o, self.w_o, out=out[0])
+
+    def forward_open(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], outs) -> None:
+        """The activations in front of the output product (normalised, gated, weighted) into ``outs[0]``."""
         state = self._state_of(cache)
         st, proj = self.stacked, self.stacked.project(x)
-        o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
+        o = outs[0]
         ops.matrix_memory_scan(st.cut(proj, "q"), st.cut(proj, "k"), st.cut(proj, "v"), st.cut(proj, "i"), st.cut(proj, "f"),
                                self.b_i, self.b_f, self.cap, state, step, self.num_heads, self.dk, self.dv, o, self.norm_w,
                                st.cut(proj, "g"), self.eps, self.out_scale)
-        ops.linear(o, self.w_o, out=out[0])
 
 
 class GatedDeltaRule(_StateMixer):
@@ -154,18 +162,25 @@ class GatedDeltaRule(_StateMixer):
         self.w_second, self.w_o = both.contiguous(), tensors["o"]
         self.rate_log, self.dt_bias, self.norm_w = tensors["A_log"], tensors["dt_bias"], tensors["norm"]
 
+    def output_weights(self):
+        return [self.w_o]
+
     def forward_into(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], out: torch.Tensor) -> None:
+        o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
+        self.forward_open(x, step, cache, [o])
+        ops.linear(o, self.w_o, out=out[0])
+
+    def forward_open(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], outs) -> None:
         state = self._state_of(cache)
         st, proj = self.stacked, self.stacked.project(x)
         G, H, dk, dv = self.num_kv_heads, self.num_heads, self.dk, self.dv
         qkv = ops.short_conv_silu(st.cut(proj, "q", "v"), self.conv_w, state[:, self.memory:], step)
         second = ops.linear(st.cut(proj, "a1", "g1"), self.w_second, out_dtype=torch.float32)
         step_pre, gate = second[:, :H * dk], second[:, H * dk:]
-        o = torch.empty((x.shape[0], H * dv), dtype=self.runtime.dtype, device=x.device)
+        o = outs[0]
         ops.gated_delta_scan(qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], st.cut(proj, "b"), step_pre,
                              self.dt_bias, self.rate_log, state[:, :self.memory], step, H, G, dk, dv, o, self.norm_w, gate,
                              self.eps, self.out_scale)
-        ops.linear(o, self.w_o, out=out[0])
 
 
 class SideBySide(Mixer):
@@ -202,6 +217,20 @@ class SideBySide(Mixer):
         for (_, c), sub in zip(self.children, cache.parts):
             c.forward_into(x, step, sub, out[at:at + c.output_parts])
             at += c.output_parts
+
+    def output_weights(self):
+        if not all(hasattr(c, "output_weights") for _, c in self.children):
+            return None
+        return [w for _, c in self.children for w in c.output_weights()]
+
+    def forward_open(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], outs) -> None:
+        if cache is None or cache.kind != "several" or len(cache.parts) != len(self.children):
+            raise ValueError("side_by_side needs one cache per child")
+        at = 0
+        for (_, c), sub in zip(self.children, cache.parts):
+            n = len(c.output_weights())
+            c.forward_open(x, step, sub, outs[at:at + n])
+            at += n
 
     def forward(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache]) -> torch.Tensor:
         out = torch.empty((self.output_parts, x.shape[0], self.hidden_size), dtype=torch.float32, device=x.device)

@@ -430,6 +430,33 @@ def test_trace_program_replays_a_schedule(folders, tmp_path):
     kc.check_rows(rows, folders[name], {"a": a, "b": b}, "float32", "trace")
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_one_output_product_per_block_equals_one_per_producer(dtype, folders, models):
+    """A block multiplies [attention | delta rule | feed-forward] by the stacked output matrices once; switched off, every
+    producer multiplies its own and the next norm adds the summands.  The same sum in another order."""
+    from coheryn_ai_studio_b200 import ops
+    name = "K1"
+    layer = models(name, dtype).layers[0]
+    assert layer._joined_output() and layer._joined_output()[0].shape[1] == 4 * 32 + 4 * 24 + 96
+    assert not models("K4", dtype).layers[0]._joined_output()          # a piece of 90 columns: no 16-byte boundaries
+    seq = kc.prompt(66, 40, vocab(name))
+    rows = {}
+    try:
+        for on in (True, False):
+            ops.set_joined_output(on)
+            r = kc.noisy_replay(folders[name], dtype, 64, models(name, dtype))
+            r.step([("r", seq[:33], list(range(33)))])
+            for t in range(33, 40):
+                r.step([("r", [seq[t]], [0])])
+            rows[on] = r.rows
+    finally:
+        ops.set_joined_output(True)
+    for key, row in rows[True].items():
+        d = np.abs(row - rows[False][key]).max() / max(1.0, float(np.std(row)))
+        assert d <= (2e-5 if dtype == "float32" else 0.05), (key, d)
+    kc.check_rows(rows[False], folders[name], {"r": seq}, dtype, "summands")
+
+
 def test_command_line_runs_and_traces_the_design(folders):
     """`coheryn run` (greedy tokens) and `coheryn trace` (every layer run's output and the logits per position) on a folder
     of this design, and the Python entry point, against the plain implementation."""
