@@ -232,6 +232,60 @@ struct DeltaIn {
   int heads, kv_heads, dk, dv;
 };
 
+// The tokens of a staged chunk, one after the other, for the thread's part of S (see ScanShape).
+template <typename L, int CP, int SPLIT>
+__device__ __forceinline__ void delta_tokens(float (&S)[CP][L::DP], const float* qs, const float* ks, const float* gs, const float* vs,
+                                             const float* betas, float* os, int nt, int part, int col0, int dvp) {
+  constexpr int DP = L::DP, ROW = L::ROW;
+  // The vectors of token i + 1 are fetched into registers before token i is worked on: the stores of a token's
+  // outputs would otherwise hold the next token's loads back.
+  float4 kc[DP / 4], gc[DP / 4], qc[DP / 4];
+  scan_fetch<DP>(kc, ks + part * L::STRIDE);
+  scan_fetch<DP>(gc, gs + part * L::STRIDE);
+  scan_fetch<DP>(qc, qs + part * L::STRIDE);
+  for (int i = 0; i < nt; ++i) {
+    float4 kn[DP / 4], gn[DP / 4], qn[DP / 4];
+    const int nx = min(i + 1, nt - 1) * ROW + part * L::STRIDE;
+    scan_fetch<DP>(kn, ks + nx); scan_fetch<DP>(gn, gs + nx); scan_fetch<DP>(qn, qs + nx);
+    float dot[CP][2];
+#pragma unroll
+    for (int c = 0; c < CP; ++c) dot[c][0] = dot[c][1] = 0.f;
+#pragma unroll
+    for (int d = 0; d < DP / 4; ++d) {
+      const float4 gg = gc[d], kk = kc[d];
+#pragma unroll
+      for (int c = 0; c < CP; ++c) {
+        S[c][4 * d] *= gg.x; S[c][4 * d + 1] *= gg.y; S[c][4 * d + 2] *= gg.z; S[c][4 * d + 3] *= gg.w;
+        dot[c][0] = fmaf(S[c][4 * d], kk.x, dot[c][0]); dot[c][1] = fmaf(S[c][4 * d + 1], kk.y, dot[c][1]);
+        dot[c][0] = fmaf(S[c][4 * d + 2], kk.z, dot[c][0]); dot[c][1] = fmaf(S[c][4 * d + 3], kk.w, dot[c][1]);
+      }
+    }
+    float u[CP];
+#pragma unroll
+    for (int c = 0; c < CP; ++c) u[c] = betas[i] * (vs[i * dvp + col0 + c] - split_sum<SPLIT>(dot[c][0] + dot[c][1]));
+#pragma unroll
+    for (int c = 0; c < CP; ++c) dot[c][0] = dot[c][1] = 0.f;
+#pragma unroll
+    for (int d = 0; d < DP / 4; ++d) {
+      const float4 kk = kc[d], qq = qc[d];
+#pragma unroll
+      for (int c = 0; c < CP; ++c) {
+        S[c][4 * d] = fmaf(kk.x, u[c], S[c][4 * d]); S[c][4 * d + 1] = fmaf(kk.y, u[c], S[c][4 * d + 1]);
+        S[c][4 * d + 2] = fmaf(kk.z, u[c], S[c][4 * d + 2]); S[c][4 * d + 3] = fmaf(kk.w, u[c], S[c][4 * d + 3]);
+        dot[c][0] = fmaf(S[c][4 * d], qq.x, dot[c][0]); dot[c][1] = fmaf(S[c][4 * d + 1], qq.y, dot[c][1]);
+        dot[c][0] = fmaf(S[c][4 * d + 2], qq.z, dot[c][0]); dot[c][1] = fmaf(S[c][4 * d + 3], qq.w, dot[c][1]);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < CP; ++c) {
+      const float o = split_sum<SPLIT>(dot[c][0] + dot[c][1]);
+      if (part == 0) os[i * dvp + col0 + c] = o;
+    }
+#pragma unroll
+    for (int d = 0; d < DP / 4; ++d) { kc[d] = kn[d]; gc[d] = gn[d]; qc[d] = qn[d]; }
+  }
+}
+
 template <int DK, int CT, int SPLIT, int CP>
 __global__ void __launch_bounds__(512) gated_delta_scan_kernel(DeltaIn P, HeadOut E) {
   using L = ScanShape<DK, SPLIT>;
@@ -294,57 +348,118 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(DeltaIn P, HeadOu
       for (int d = lane; d < DK; d += 32) { qs[i * ROW + L::at(d)] *= iq; ks[i * ROW + L::at(d)] *= ik; }
     }
     __syncthreads();
-    // The vectors of token i + 1 are fetched into registers before token i is worked on: the stores of a token's
-    // outputs would otherwise hold the next token's loads back.
-    float4 kc[DP / 4], gc[DP / 4], qc[DP / 4];
-    scan_fetch<DP>(kc, ks + part * L::STRIDE);
-    scan_fetch<DP>(gc, gs + part * L::STRIDE);
-    scan_fetch<DP>(qc, qs + part * L::STRIDE);
-    for (int i = 0; i < nt; ++i) {
-      float4 kn[DP / 4], gn[DP / 4], qn[DP / 4];
-      const int nx = min(i + 1, nt - 1) * ROW + part * L::STRIDE;
-      scan_fetch<DP>(kn, ks + nx); scan_fetch<DP>(gn, gs + nx); scan_fetch<DP>(qn, qs + nx);
-      float dot[CP][2];
-#pragma unroll
-      for (int c = 0; c < CP; ++c) dot[c][0] = dot[c][1] = 0.f;
-#pragma unroll
-      for (int d = 0; d < DP / 4; ++d) {
-        const float4 gg = gc[d], kk = kc[d];
-#pragma unroll
-        for (int c = 0; c < CP; ++c) {
-          S[c][4 * d] *= gg.x; S[c][4 * d + 1] *= gg.y; S[c][4 * d + 2] *= gg.z; S[c][4 * d + 3] *= gg.w;
-          dot[c][0] = fmaf(S[c][4 * d], kk.x, dot[c][0]); dot[c][1] = fmaf(S[c][4 * d + 1], kk.y, dot[c][1]);
-          dot[c][0] = fmaf(S[c][4 * d + 2], kk.z, dot[c][0]); dot[c][1] = fmaf(S[c][4 * d + 3], kk.w, dot[c][1]);
-        }
-      }
-      float u[CP];
-#pragma unroll
-      for (int c = 0; c < CP; ++c) u[c] = betas[i] * (vs[i * dvp + col0 + c] - split_sum<SPLIT>(dot[c][0] + dot[c][1]));
-#pragma unroll
-      for (int c = 0; c < CP; ++c) dot[c][0] = dot[c][1] = 0.f;
-#pragma unroll
-      for (int d = 0; d < DP / 4; ++d) {
-        const float4 kk = kc[d], qq = qc[d];
-#pragma unroll
-        for (int c = 0; c < CP; ++c) {
-          S[c][4 * d] = fmaf(kk.x, u[c], S[c][4 * d]); S[c][4 * d + 1] = fmaf(kk.y, u[c], S[c][4 * d + 1]);
-          S[c][4 * d + 2] = fmaf(kk.z, u[c], S[c][4 * d + 2]); S[c][4 * d + 3] = fmaf(kk.w, u[c], S[c][4 * d + 3]);
-          dot[c][0] = fmaf(S[c][4 * d], qq.x, dot[c][0]); dot[c][1] = fmaf(S[c][4 * d + 1], qq.y, dot[c][1]);
-          dot[c][0] = fmaf(S[c][4 * d + 2], qq.z, dot[c][0]); dot[c][1] = fmaf(S[c][4 * d + 3], qq.w, dot[c][1]);
-        }
-      }
-#pragma unroll
-      for (int c = 0; c < CP; ++c) {
-        const float o = split_sum<SPLIT>(dot[c][0] + dot[c][1]);
-        if (part == 0) os[i * dvp + col0 + c] = o;
-      }
-#pragma unroll
-      for (int d = 0; d < DP / 4; ++d) { kc[d] = kn[d]; gc[d] = gn[d]; qc[d] = qn[d]; }
-    }
+    delta_tokens<L, CP, SPLIT>(S, qs, ks, gs, vs, betas, os, nt, part, col0, dvp);
     __syncthreads();
     if (E.raw) raw_out_chunk(E, os, dvp, dv, colbase, nt, row0, h);
     else head_out_chunk(E, os, dvp, dv, nt, row0, h);
     __syncthreads();
+  }
+  scan_state_store<CP, DP>(S, S_state, d0, colbase + col0, dk, dv);
+}
+
+// ---------------------------------------------------------------------------------
+// The same scan for long prompts: what the plain kernel computes while it stages a chunk (unit-norm q and k, decays, beta)
+// is made ONCE per token by delta_prepare_kernel, parallel over the tokens, so that this kernel stages by asynchronous
+// copies, two chunks deep, and the CTAs that share a head (64 value channels each) repeat nothing but copies.
+// prep: [T][kv_heads*dk (q) | kv_heads*dk (k) | heads*dk (decay) | heads (beta)].
+// ---------------------------------------------------------------------------------
+__device__ __forceinline__ void cp_async4(float* smem_dst, const float* src) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(smem_dst);
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(a), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit_group() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_group() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__global__ void __launch_bounds__(128) delta_prepare_kernel(DeltaIn P, float* __restrict__ prep, long ld_prep) {
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const size_t t = blockIdx.x;
+  const int dk = P.dk, G = P.kv_heads, H = P.heads;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  float* out = prep + t * ld_prep;
+  const float q_scale = 1.0f / sqrtf((float)dk);
+  for (int g = warp; g < G; g += warps) {          // the same sums, in the same order, as the plain kernel's staging
+    const float* q = P.q + t * P.ld_qkv + (size_t)g * dk;
+    const float* k = P.k + t * P.ld_qkv + (size_t)g * dk;
+    float sq = 0.f, sk = 0.f;
+    for (int d = lane; d < dk; d += 32) { sq = fmaf(q[d], q[d], sq); sk = fmaf(k[d], k[d], sk); }
+    sq = co_warp_sum(sq); sk = co_warp_sum(sk);
+    const float iq = q_scale / sqrtf(sq + 1e-6f), ik = 1.0f / sqrtf(sk + 1e-6f);
+    for (int d = lane; d < dk; d += 32) { out[(size_t)g * dk + d] = q[d] * iq; out[(size_t)(G + g) * dk + d] = k[d] * ik; }
+  }
+  for (int e = threadIdx.x; e < H * dk; e += blockDim.x) {
+    const float rate = expf(co_load_any(P.rate_log, P.rate_log_dtype, e / dk));
+    const float z = P.step[t * P.ld_step + e] + co_load_any(P.step_bias, P.step_bias_dtype, e);
+    out[(size_t)2 * G * dk + e] = expf(-rate * rc_softplus(z));
+  }
+  for (int e = threadIdx.x; e < H; e += blockDim.x) out[(size_t)(2 * G + H) * dk + e] = rc_sigmoid(P.beta[t * P.ld_beta + e]);
+}
+
+template <int DK, int CT, int SPLIT, int CP>
+__global__ void __launch_bounds__(512) gated_delta_scan_pre_kernel(DeltaIn P, HeadOut E, const float* __restrict__ prep, long ld_prep) {
+  using L = ScanShape<DK, SPLIT>;
+  constexpr int DP = L::DP, ROW = L::ROW;
+  extern __shared__ __align__(16) float smem[];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int part = threadIdx.x % SPLIT, col0 = (threadIdx.x / SPLIT) * CP, d0 = part * DP;
+  const int dk = P.dk, dv = P.dv, dvp = (blockDim.x / SPLIT) * CP;
+  const int colbase = blockIdx.z * dvp;
+  const int start = P.cu_q[r], len = P.cu_q[r + 1] - start;
+  if (len <= 0) return;
+  const int g = h / (P.heads / P.kv_heads), G = P.kv_heads, H = P.heads;
+  const int STAGE = 3 * CT * ROW + CT * dvp + CT;      // floats of one staged chunk: q, k, decay rows, values, betas
+  float* os = smem + 2 * STAGE;                        // [CT][dvp]
+  float* S_state = P.state + (size_t)P.state_slots[r] * P.state_stride + (size_t)h * dk * dv;
+  float S[CP][DP];
+  scan_state_load<CP, DP>(S, S_state, d0, colbase + col0, dk, dv);
+  // the padding of both stages once: channels beyond dk (q = k = 0, decay 1) and columns beyond dv
+  for (int e = threadIdx.x; e < 2 * STAGE; e += blockDim.x) {
+    const int w = e % STAGE;
+    smem[e] = (w >= 2 * CT * ROW && w < 3 * CT * ROW) ? 1.f : 0.f;
+  }
+  __syncthreads();
+  auto stage = [&](int c0, int b) {
+    const int nt = min(CT, len - c0), row0 = start + c0;
+    float* qs = smem + b * STAGE;
+    float* ks = qs + CT * ROW;
+    float* gs = ks + CT * ROW;
+    float* vs = gs + CT * ROW;
+    float* betas = vs + CT * dvp;
+    for (int e = threadIdx.x; e < nt * dk; e += blockDim.x) {
+      const int i = e / dk, d = e % dk;
+      const float* src = prep + (size_t)(row0 + i) * ld_prep;
+      const int o = i * ROW + L::at(d);
+      cp_async4(qs + o, src + (size_t)g * dk + d);
+      cp_async4(ks + o, src + (size_t)(G + g) * dk + d);
+      cp_async4(gs + o, src + (size_t)(2 * G + h) * dk + d);
+    }
+    for (int e = threadIdx.x; e < nt * dvp; e += blockDim.x) {
+      const int i = e / dvp, c = e % dvp;
+      if (colbase + c < dv) cp_async4(vs + e, P.v + (size_t)(row0 + i) * P.ld_qkv + (size_t)h * dv + colbase + c);
+    }
+    if (threadIdx.x < nt) cp_async4(betas + threadIdx.x, prep + (size_t)(row0 + threadIdx.x) * ld_prep + (size_t)(2 * G + H) * dk + h);
+    cp_async_commit_group();
+  };
+  stage(0, 0);
+  int b = 0;
+  for (int c0 = 0; c0 < len; c0 += CT, b ^= 1) {
+    const int nt = min(CT, len - c0), row0 = start + c0;
+    if (c0 + CT < len) { stage(c0 + CT, b ^ 1); cp_async_wait_group<1>(); }
+    else cp_async_wait_group<0>();
+    __syncthreads();
+    const float* qs = smem + b * STAGE;
+    const float* ks = qs + CT * ROW;
+    const float* gs = ks + CT * ROW;
+    const float* vs = gs + CT * ROW;
+    const float* betas = vs + CT * dvp;
+    delta_tokens<L, CP, SPLIT>(S, qs, ks, gs, vs, betas, os, nt, part, col0, dvp);
+    __syncthreads();
+    if (E.raw) raw_out_chunk(E, os, dvp, dv, colbase, nt, row0, h);
+    else head_out_chunk(E, os, dvp, dv, nt, row0, h);
+    __syncthreads();       // the outputs are read, and this stage may be filled again two chunks on
   }
   scan_state_store<CP, DP>(S, S_state, d0, colbase + col0, dk, dv);
 }
@@ -361,6 +476,71 @@ struct MemoryIn {
   const int* cu_q; const int* state_slots;
   int heads, dk, dv;
 };
+
+// The scalar part of the recurrence for a staged chunk, by one warp, token by token: maximum, the two factors, the
+// normaliser n (a lane holds n[lane + 32 j]) and the denominator.  lf and li come in as the log gates and leave as a and b.
+template <typename L, int NJ>
+__device__ __forceinline__ void memory_scalars(float (&nreg)[NJ], float& m, const float* qs, const float* ks, float* li, float* lf,
+                                               float* den, int nt, int lane) {
+  constexpr int DK = L::DP * (L::ROW / L::STRIDE), ROW = L::ROW;
+  // the scalar part of the recurrence, token by token: maximum, the two factors, normaliser and denominator
+  for (int i = 0; i < nt; ++i) {
+    const float f = lf[i], in = li[i];
+    const float m_new = fmaxf(f + m, in);
+    const float a = expf(f + m - m_new), b = expf(in - m_new);
+    m = m_new;
+    float sum = 0.f;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) {
+      const int d = lane + 32 * j;
+      if (d < DK) {
+        nreg[j] = fmaf(b, ks[i * ROW + L::at(d)], a * nreg[j]);
+        sum = fmaf(nreg[j], qs[i * ROW + L::at(d)], sum);
+      }
+    }
+    sum = co_warp_sum(sum);
+    __syncwarp();
+    if (lane == 0) { lf[i] = a; li[i] = b; den[i] = fmaxf(fabsf(sum), expf(-m)) + 1e-6f; }
+  }
+}
+
+// The tokens of a staged chunk for the thread's part of S: li holds b = exp(i - m), lf holds a = exp(f + m' - m), den the
+// denominators, as the scalar phase left them.
+template <typename L, int CP, int SPLIT>
+__device__ __forceinline__ void memory_tokens(float (&S)[CP][L::DP], const float* qs, const float* ks, const float* vs, const float* li,
+                                              const float* lf, const float* den, float* os, int nt, int part, int col0, int dvp) {
+  constexpr int DP = L::DP, ROW = L::ROW;
+  float4 kc[DP / 4], qc[DP / 4];        // token i + 1 is fetched before token i is worked on (see the delta rule)
+  scan_fetch<DP>(kc, ks + part * L::STRIDE);
+  scan_fetch<DP>(qc, qs + part * L::STRIDE);
+  for (int i = 0; i < nt; ++i) {
+    float4 kn[DP / 4], qn[DP / 4];
+    const int nx = min(i + 1, nt - 1) * ROW + part * L::STRIDE;
+    scan_fetch<DP>(kn, ks + nx); scan_fetch<DP>(qn, qs + nx);
+    const float a = lf[i];
+    float bv[CP], o[CP][2];
+#pragma unroll
+    for (int c = 0; c < CP; ++c) { bv[c] = li[i] * vs[i * dvp + col0 + c]; o[c][0] = o[c][1] = 0.f; }
+#pragma unroll
+    for (int d = 0; d < DP / 4; ++d) {
+      const float4 kk = kc[d], qq = qc[d];
+#pragma unroll
+      for (int c = 0; c < CP; ++c) {
+        S[c][4 * d] = fmaf(bv[c], kk.x, a * S[c][4 * d]); S[c][4 * d + 1] = fmaf(bv[c], kk.y, a * S[c][4 * d + 1]);
+        S[c][4 * d + 2] = fmaf(bv[c], kk.z, a * S[c][4 * d + 2]); S[c][4 * d + 3] = fmaf(bv[c], kk.w, a * S[c][4 * d + 3]);
+        o[c][0] = fmaf(S[c][4 * d], qq.x, o[c][0]); o[c][1] = fmaf(S[c][4 * d + 1], qq.y, o[c][1]);
+        o[c][0] = fmaf(S[c][4 * d + 2], qq.z, o[c][0]); o[c][1] = fmaf(S[c][4 * d + 3], qq.w, o[c][1]);
+      }
+    }
+#pragma unroll
+    for (int c = 0; c < CP; ++c) {
+      const float y = split_sum<SPLIT>(o[c][0] + o[c][1]);
+      if (part == 0) os[i * dvp + col0 + c] = y / den[i];
+    }
+#pragma unroll
+    for (int d = 0; d < DP / 4; ++d) { kc[d] = kn[d]; qc[d] = qn[d]; }
+  }
+}
 
 template <int DK, int CT, int SPLIT, int CP>
 __global__ void __launch_bounds__(512) matrix_memory_scan_kernel(MemoryIn P, HeadOut E) {
@@ -422,58 +602,9 @@ __global__ void __launch_bounds__(512) matrix_memory_scan_kernel(MemoryIn P, Hea
       lf[threadIdx.x] = -rc_softplus(-z);          // log sigmoid
     }
     __syncthreads();
-    if (warp == 0) {
-      // the scalar part of the recurrence, token by token: maximum, the two factors, normaliser and denominator
-      for (int i = 0; i < nt; ++i) {
-        const float f = lf[i], in = li[i];
-        const float m_new = fmaxf(f + m, in);
-        const float a = expf(f + m - m_new), b = expf(in - m_new);
-        m = m_new;
-        float sum = 0.f;
-#pragma unroll
-        for (int j = 0; j < NJ; ++j) {
-          const int d = lane + 32 * j;
-          if (d < DK) {
-            nreg[j] = fmaf(b, ks[i * ROW + L::at(d)], a * nreg[j]);
-            sum = fmaf(nreg[j], qs[i * ROW + L::at(d)], sum);
-          }
-        }
-        sum = co_warp_sum(sum);
-        __syncwarp();
-        if (lane == 0) { lf[i] = a; li[i] = b; den[i] = fmaxf(fabsf(sum), expf(-m)) + 1e-6f; }
-      }
-    }
+    if (warp == 0) memory_scalars<L, NJ>(nreg, m, qs, ks, li, lf, den, nt, lane);
     __syncthreads();
-    float4 kc[DP / 4], qc[DP / 4];        // token i + 1 is fetched before token i is worked on (see the delta rule)
-    scan_fetch<DP>(kc, ks + part * L::STRIDE);
-    scan_fetch<DP>(qc, qs + part * L::STRIDE);
-    for (int i = 0; i < nt; ++i) {
-      float4 kn[DP / 4], qn[DP / 4];
-      const int nx = min(i + 1, nt - 1) * ROW + part * L::STRIDE;
-      scan_fetch<DP>(kn, ks + nx); scan_fetch<DP>(qn, qs + nx);
-      const float a = lf[i];
-      float bv[CP], o[CP][2];
-#pragma unroll
-      for (int c = 0; c < CP; ++c) { bv[c] = li[i] * vs[i * dvp + col0 + c]; o[c][0] = o[c][1] = 0.f; }
-#pragma unroll
-      for (int d = 0; d < DP / 4; ++d) {
-        const float4 kk = kc[d], qq = qc[d];
-#pragma unroll
-        for (int c = 0; c < CP; ++c) {
-          S[c][4 * d] = fmaf(bv[c], kk.x, a * S[c][4 * d]); S[c][4 * d + 1] = fmaf(bv[c], kk.y, a * S[c][4 * d + 1]);
-          S[c][4 * d + 2] = fmaf(bv[c], kk.z, a * S[c][4 * d + 2]); S[c][4 * d + 3] = fmaf(bv[c], kk.w, a * S[c][4 * d + 3]);
-          o[c][0] = fmaf(S[c][4 * d], qq.x, o[c][0]); o[c][1] = fmaf(S[c][4 * d + 1], qq.y, o[c][1]);
-          o[c][0] = fmaf(S[c][4 * d + 2], qq.z, o[c][0]); o[c][1] = fmaf(S[c][4 * d + 3], qq.w, o[c][1]);
-        }
-      }
-#pragma unroll
-      for (int c = 0; c < CP; ++c) {
-        const float y = split_sum<SPLIT>(o[c][0] + o[c][1]);
-        if (part == 0) os[i * dvp + col0 + c] = y / den[i];
-      }
-#pragma unroll
-      for (int d = 0; d < DP / 4; ++d) { kc[d] = kn[d]; qc[d] = qn[d]; }
-    }
+    memory_tokens<L, CP, SPLIT>(S, qs, ks, vs, li, lf, den, os, nt, part, col0, dvp);
     __syncthreads();
     if (E.raw) raw_out_chunk(E, os, dvp, dv, colbase, nt, row0, h);
     else head_out_chunk(E, os, dvp, dv, nt, row0, h);
@@ -482,6 +613,104 @@ __global__ void __launch_bounds__(512) matrix_memory_scan_kernel(MemoryIn P, Hea
   scan_state_store<CP, DP>(S, S_state, d0, colbase + col0, dk, dv);
   if (warp == 0 && blockIdx.z == 0) {
     // with the head's columns split over CTAs the others may not have read n and m yet: they go to the side
+    float* n_to = E.nm_next ? E.nm_next + ((size_t)r * P.heads + h) * (dk + 1) : n_state;
+    float* m_to = E.nm_next ? n_to + dk : m_state;
+#pragma unroll
+    for (int j = 0; j < NJ; ++j)
+      if (lane + 32 * j < dk) n_to[lane + 32 * j] = nreg[j];
+    if (lane == 0) *m_to = m;
+  }
+}
+
+// The matrix memory for long prompts: chunks of 16 tokens staged by asynchronous copies, two deep (what is computed while
+// staging is little here: q times 1 / sqrt(dk) and the two log gates of a token, done when a chunk has landed).
+template <int DK, int CT, int SPLIT, int CP>
+__global__ void __launch_bounds__(512) matrix_memory_scan_pre_kernel(MemoryIn P, HeadOut E) {
+  using L = ScanShape<DK, SPLIT>;
+  constexpr int DP = L::DP, ROW = L::ROW;
+  extern __shared__ __align__(16) float smem[];
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int r = blockIdx.x, h = blockIdx.y;
+  const int part = threadIdx.x % SPLIT, col0 = (threadIdx.x / SPLIT) * CP, d0 = part * DP;
+  const int dk = P.dk, dv = P.dv, dvp = (blockDim.x / SPLIT) * CP;
+  const int colbase = blockIdx.z * dvp;
+  const int start = P.cu_q[r], len = P.cu_q[r + 1] - start;
+  if (len <= 0) return;
+  const int STAGE = 2 * CT * ROW + CT * dvp + 2 * CT;      // floats of one staged chunk: q, k rows, values, the two gates
+  float* os = smem + 2 * STAGE;                            // [CT][dvp]
+  float* den = os + CT * dvp;                              // [CT]
+  float* slot = P.state + (size_t)P.state_slots[r] * P.state_stride;
+  float* S_state = slot + (size_t)h * dk * dv;
+  float* n_state = slot + (size_t)P.heads * dk * dv + (size_t)h * dk;
+  float* m_state = slot + (size_t)P.heads * dk * dv + (size_t)P.heads * dk + h;
+  float S[CP][DP];
+  scan_state_load<CP, DP>(S, S_state, d0, colbase + col0, dk, dv);
+  constexpr int NJ = (DK + 31) / 32;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float nreg[NJ];
+  float m = 0.f;
+  if (warp == 0) {
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) nreg[j] = (lane + 32 * j < dk) ? n_state[lane + 32 * j] : 0.f;
+    m = *m_state;
+  }
+  const float q_scale = 1.0f / sqrtf((float)dk);
+  const float bi = co_load_any(P.bias_i, P.bias_dtype, h), bf = co_load_any(P.bias_f, P.bias_dtype, h);
+  for (int e = threadIdx.x; e < 2 * STAGE; e += blockDim.x) smem[e] = 0.f;      // the padding of both stages, once
+  __syncthreads();
+  auto stage = [&](int c0, int b) {
+    const int nt = min(CT, len - c0), row0 = start + c0;
+    float* qs = smem + b * STAGE;
+    float* ks = qs + CT * ROW;
+    float* vs = ks + CT * ROW;
+    float* gates = vs + CT * dvp;
+    for (int e = threadIdx.x; e < nt * dk; e += blockDim.x) {
+      const int i = e / dk, d = e % dk;
+      const size_t row = (size_t)(row0 + i);
+      const int o = i * ROW + L::at(d);
+      cp_async4(qs + o, P.q + row * P.ld + (size_t)h * dk + d);
+      cp_async4(ks + o, P.k + row * P.ld + (size_t)h * dk + d);
+    }
+    for (int e = threadIdx.x; e < nt * dvp; e += blockDim.x) {
+      const int i = e / dvp, c = e % dvp;
+      if (colbase + c < dv) cp_async4(vs + e, P.v + (size_t)(row0 + i) * P.ld + (size_t)h * dv + colbase + c);
+    }
+    if (threadIdx.x < nt) {
+      cp_async4(gates + threadIdx.x, P.gi + (size_t)(row0 + threadIdx.x) * P.ld_gate + h);
+      cp_async4(gates + CT + threadIdx.x, P.gf + (size_t)(row0 + threadIdx.x) * P.ld_gate + h);
+    }
+    cp_async_commit_group();
+  };
+  stage(0, 0);
+  int b = 0;
+  for (int c0 = 0; c0 < len; c0 += CT, b ^= 1) {
+    const int nt = min(CT, len - c0), row0 = start + c0;
+    if (c0 + CT < len) { stage(c0 + CT, b ^ 1); cp_async_wait_group<1>(); }
+    else cp_async_wait_group<0>();
+    __syncthreads();
+    float* qs = smem + b * STAGE;
+    float* ks = qs + CT * ROW;
+    float* vs = ks + CT * ROW;
+    float* li = vs + CT * dvp;
+    float* lf = li + CT;
+    for (int e = threadIdx.x; e < nt * dk; e += blockDim.x) qs[(e / dk) * ROW + L::at(e % dk)] *= q_scale;
+    if (threadIdx.x < nt) {
+      li[threadIdx.x] = P.cap * tanhf((li[threadIdx.x] + bi) / P.cap);
+      const float z = P.cap * tanhf((lf[threadIdx.x] + bf) / P.cap);
+      lf[threadIdx.x] = -rc_softplus(-z);
+    }
+    __syncthreads();
+    if (warp == 0) memory_scalars<L, NJ>(nreg, m, qs, ks, li, lf, den, nt, lane);
+    __syncthreads();
+    memory_tokens<L, CP, SPLIT>(S, qs, ks, vs, li, lf, den, os, nt, part, col0, dvp);
+    __syncthreads();
+    if (E.raw) raw_out_chunk(E, os, dvp, dv, colbase, nt, row0, h);
+    else head_out_chunk(E, os, dvp, dv, nt, row0, h);
+    __syncthreads();
+  }
+  scan_state_store<CP, DP>(S, S_state, d0, colbase + col0, dk, dv);
+  if (warp == 0 && blockIdx.z == 0) {
     float* n_to = E.nm_next ? E.nm_next + ((size_t)r * P.heads + h) * (dk + 1) : n_state;
     float* m_to = E.nm_next ? n_to + dk : m_state;
 #pragma unroll
@@ -603,21 +832,35 @@ CO_EXPORT int coheryn_gated_delta_scan(
     float out_scale, int total_tokens, float* scratch, long scratch_floats, cudaStream_t stream) {
   if (B <= 0) return 0;
   if (!scan_shape_ok("gated_delta_scan", heads, dk, dv)) return 1;
-  const int slices = scan_slices(B, heads, dv, total_tokens, scratch, scratch_floats, 0);
+  const long ld_prep = (long)2 * kv_heads * dk + (long)heads * dk + heads;     // per token: q, k, decays, beta
+  const int slices = scan_slices(B, heads, dv, total_tokens, scratch, scratch_floats, (long)total_tokens * ld_prep);
+  float* prep = slices > 1 ? scratch + (long)total_tokens * heads * dv : nullptr;
   if (kv_heads < 1 || heads % kv_heads) CO_FAIL("gated_delta_scan: %d heads do not group over %d q/k heads", heads, kv_heads);
   DeltaIn P{q, k, v, ld_qkv, beta, ld_beta, step, ld_step, step_bias, step_bias_dtype, rate_log, rate_log_dtype, state,
             state_stride, cu_q, state_slots, heads, kv_heads, dk, dv};
   HeadOut E{out, out_dtype, ldo, weight, weight_dtype, weight_stride, gate, ldg, eps, out_scale,
             slices > 1 ? scratch : nullptr, (long)heads * dv, nullptr};
+  if (slices > 1) {
+    co_launch(delta_prepare_kernel, dim3(total_tokens), dim3(128), 0, stream, P, prep, ld_prep);
+    CO_CHECK_LAUNCH("delta_prepare");
+  }
 #define LAUNCH_CP(D, WIDE)                                                                                     \
   {                                                                                                            \
     constexpr int CT = chunk_tokens(D), SP = scan_split(D), CP = scan_columns(D, WIDE), ROW = ScanShape<D, SP>::ROW; \
-    const int cols = slices > 1 ? SLICE_COLUMNS : dv;                                                                     \
+    const int cols = slices > 1 ? SLICE_COLUMNS : dv;                                                          \
     const int threads = ((cols + CP - 1) / CP * SP + 31) / 32 * 32, dvp = threads / SP * CP;                   \
-    const size_t smem = ((size_t)3 * CT * ROW + (size_t)2 * CT * dvp + CT) * sizeof(float);                                                               \
-    auto kern = gated_delta_scan_kernel<D, CT, SP, CP>;                                                                          \
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-    co_launch_ex(true, kern, dim3(B, heads, slices > 1 ? (dv + dvp - 1) / dvp : 1), dim3(threads), smem, stream, P, E); \
+    if (slices > 1) {   /* a long prompt: prepared inputs, asynchronous staging of 16 tokens, two deep */          \
+      constexpr int CA = 16;                                                                                   \
+      const size_t smem = ((size_t)2 * (3 * CA * ROW + CA * dvp + CA) + (size_t)CA * dvp) * sizeof(float);     \
+      auto kern = gated_delta_scan_pre_kernel<D, CA, SP, CP>;                                                  \
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      co_launch_ex(true, kern, dim3(B, heads, (dv + dvp - 1) / dvp), dim3(threads), smem, stream, P, E, (const float*)prep, ld_prep); \
+    } else {                                                                                                   \
+      const size_t smem = ((size_t)3 * CT * ROW + (size_t)2 * CT * dvp + CT) * sizeof(float);                  \
+      auto kern = gated_delta_scan_kernel<D, CT, SP, CP>;                                                      \
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      co_launch_ex(true, kern, dim3(B, heads, 1), dim3(threads), smem, stream, P, E);                          \
+    }                                                                                                          \
   }
 #define LAUNCH(D) if (slices == 1 && dv * scan_split(D) > 128 * 16) LAUNCH_CP(D, true) else LAUNCH_CP(D, false)
   CO_SCAN_CASES(LAUNCH)
@@ -643,12 +886,20 @@ CO_EXPORT int coheryn_matrix_memory_scan(
 #define LAUNCH_CP(D, WIDE)                                                                                     \
   {                                                                                                            \
     constexpr int CT = chunk_tokens(D), SP = scan_split(D), CP = scan_columns(D, WIDE), ROW = ScanShape<D, SP>::ROW; \
-    const int cols = slices > 1 ? SLICE_COLUMNS : dv;                                                                     \
+    const int cols = slices > 1 ? SLICE_COLUMNS : dv;                                                          \
     const int threads = ((cols + CP - 1) / CP * SP + 31) / 32 * 32, dvp = threads / SP * CP;                   \
-    const size_t smem = ((size_t)2 * CT * ROW + (size_t)2 * CT * dvp + 3 * CT) * sizeof(float);                                                               \
-    auto kern = matrix_memory_scan_kernel<D, CT, SP, CP>;                                                                          \
-    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
-    co_launch_ex(true, kern, dim3(B, heads, slices > 1 ? (dv + dvp - 1) / dvp : 1), dim3(threads), smem, stream, P, E); \
+    if (slices > 1) {   /* a long prompt: asynchronous staging of 16 tokens, two deep */                        \
+      constexpr int CA = 16;                                                                                   \
+      const size_t smem = ((size_t)2 * (2 * CA * ROW + CA * dvp + 2 * CA) + (size_t)CA * dvp + CA) * sizeof(float); \
+      auto kern = matrix_memory_scan_pre_kernel<D, CA, SP, CP>;                                                \
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      co_launch_ex(true, kern, dim3(B, heads, (dv + dvp - 1) / dvp), dim3(threads), smem, stream, P, E);       \
+    } else {                                                                                                   \
+      const size_t smem = ((size_t)2 * CT * ROW + (size_t)2 * CT * dvp + 3 * CT) * sizeof(float);              \
+      auto kern = matrix_memory_scan_kernel<D, CT, SP, CP>;                                                    \
+      if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      co_launch_ex(true, kern, dim3(B, heads, 1), dim3(threads), smem, stream, P, E);                          \
+    }                                                                                                          \
   }
 #define LAUNCH(D) if (slices == 1 && dv * scan_split(D) > 128 * 16) LAUNCH_CP(D, true) else LAUNCH_CP(D, false)
   CO_SCAN_CASES(LAUNCH)

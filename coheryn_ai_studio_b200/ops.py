@@ -975,7 +975,7 @@ def gated_delta_scan(q, k, v, beta, step_pre, step_bias, rate_log, state, step, 
     assert step_bias.numel() == heads * dk and rate_log.numel() == heads and norm_weight.numel() == dv
     assert state.shape[1] == heads * dk * dv and out.shape == (q.shape[0], heads * dv) and out.stride(1) == 1
     lib = recurrent()
-    scratch = _scan_scratch(q.shape[0], step.num_requests, heads, dv, 0, q.device)
+    scratch = _scan_scratch(q.shape[0], step.num_requests, heads, dv, q.shape[0] * (2 * kv_heads * dk + heads * dk + heads), q.device)
     _check(lib, lib.coheryn_gated_delta_scan(
         _ptr(q), _ptr(k), _ptr(v), c_long(q.stride(0)), _ptr(beta), c_long(beta.stride(0)), _ptr(step_pre),
         c_long(step_pre.stride(0)), _ptr(step_bias), c_int(_code(step_bias)), _ptr(rate_log), c_int(_code(rate_log)),

@@ -184,6 +184,60 @@ def test_matrix_memory_kernel(heads, dk, dv, cap):
     assert np.abs(other[-1] - want[1][-1, :dv]).max() > 0.05
 
 
+@pytest.mark.parametrize("heads,dk,dv", [(2, 24, 200), (1, 128, 256), (3, 64, 72)])
+def test_scans_of_long_portions_split_a_heads_columns_over_ctas(heads, dk, dv):
+    """One request whose long portions (64 tokens and more) run as several CTAs per head, with norm and gate in a kernel of
+    their own (the delta rule from prepared inputs, staged asynchronously), and whose short portions run the one-CTA kernels:
+    both against the token-by-token recurrences, continuing each other's state."""
+    from coheryn_ai_studio_b200 import ops
+    rng = np.random.default_rng(dv)
+    cuts, eps, cap, groups = [130, 1, 70, 2, 64, 33], 1e-6, 9.0, 1
+    n = sum(cuts)
+    f = lambda *shape: rng.normal(size=shape)
+    # the delta rule
+    d = dict(q=f(n, groups * dk), k=f(n, groups * dk), v=f(n, heads * dv), beta=f(n, heads), step=f(n, heads * dk), gate=f(n, heads * dv))
+    bias, rate_log, weight = f(heads * dk), f(heads) * 0.5, f(dv)
+    q = d["q"].reshape(n, groups, dk); k = d["k"].reshape(n, groups, dk)
+    q = q / np.sqrt((q * q).sum(-1, keepdims=True) + 1e-6) * dk ** -0.5
+    k = k / np.sqrt((k * k).sum(-1, keepdims=True) + 1e-6)
+    decay = np.exp(-np.exp(rate_log)[None, :, None] * plain.softplus(d["step"] + bias).reshape(n, heads, dk))
+    o = np.stack([plain.gated_delta_rule(q[:, 0], k[:, 0], d["v"].reshape(n, heads, dv)[:, h], plain.sigmoid(d["beta"][:, h]), decay[:, h])
+                  for h in range(heads)], axis=1)
+    want = _norm_gate(o, weight, d["gate"].reshape(n, heads, dv), eps).reshape(n, heads * dv)
+    state = torch.zeros((2, heads * dk * dv), device=DEV)
+    at = 0
+    for m in cuts:
+        step = step_of([m], slots=[1])
+        cat = lambda key: dev(d[key][at:at + m])
+        qkv = torch.cat([cat("q"), cat("k"), cat("v")], dim=1)
+        out = torch.empty((m, heads * dv), device=DEV)
+        ops.gated_delta_scan(qkv[:, :groups * dk], qkv[:, groups * dk:2 * groups * dk], qkv[:, 2 * groups * dk:], cat("beta"), cat("step"),
+                             dev(bias), dev(rate_log), state, step, heads, groups, dk, dv, out, dev(weight), cat("gate"), eps)
+        ref = want[at:at + m]
+        assert np.abs(out.cpu().numpy() - ref).max() <= 3e-4 * max(1.0, np.abs(ref).max()), ("delta", at, m)
+        at += m
+    # the matrix memory
+    d = dict(q=f(n, heads * dk), k=f(n, heads * dk), v=f(n, heads * dv), gi=f(n, heads) * 2, gf=f(n, heads) * 2 + 3.0, gate=f(n, heads * dv))
+    bi, bf, weight = f(heads), f(heads), f(heads * dv)
+    li = cap * np.tanh((d["gi"] + bi) / cap); lf = plain.log_sigmoid(cap * np.tanh((d["gf"] + bf) / cap))
+    o = np.stack([plain.matrix_memory(d["q"].reshape(n, heads, dk)[:, h] * dk ** -0.5, d["k"].reshape(n, heads, dk)[:, h],
+                                      d["v"].reshape(n, heads, dv)[:, h], li[:, h], lf[:, h]) for h in range(heads)], axis=1)
+    want = plain.rms(o, eps).reshape(n, heads * dv) * weight * plain.sigmoid(d["gate"])
+    state = torch.zeros((2, heads * (dk * dv + dk + 1)), device=DEV)
+    at = 0
+    for m in cuts:
+        step = step_of([m], slots=[1])
+        cat = lambda key: dev(d[key][at:at + m])
+        qkv = torch.cat([cat("q"), cat("k"), cat("v")], dim=1)
+        gates = torch.cat([cat("gi"), cat("gf")], dim=1)
+        out = torch.empty((m, heads * dv), device=DEV)
+        ops.matrix_memory_scan(qkv[:, :heads * dk], qkv[:, heads * dk:2 * heads * dk], qkv[:, 2 * heads * dk:], gates[:, :heads], gates[:, heads:],
+                               dev(bi), dev(bf), cap, state, step, heads, dk, dv, out, dev(weight), cat("gate"), eps)
+        ref = want[at:at + m]
+        assert np.abs(out.cpu().numpy() - ref).max() <= 1e-3 * max(1.0, np.abs(ref).max()), ("memory", at, m)
+        at += m
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("dk,dv,window,page", [(16, 32, 24, 16), (32, 32, 5, 4), (64, 64, 72, 16), (48, 80, 40, 8), (128, 64, 130, 16)])
 def test_distance_bias_attention_window_edges(dtype, dk, dv, window, page):
