@@ -622,6 +622,63 @@ __global__ void __launch_bounds__(512) matrix_memory_scan_kernel(MemoryIn P, Hea
   }
 }
 
+// For long prompts the normaliser n is kept by every thread for its own part of the key channels (beside its part of S), so
+// that n . q comes out of the token loop like the columns' products and no warp walks the chunk alone first; what is left
+// of the scalar part is the running maximum and the two factors of a token: lf leaves as a, li as b, em as exp(-m).
+__device__ __forceinline__ void memory_factors(float& m, float* li, float* lf, float* em, int nt, int lane) {
+  for (int i = 0; i < nt; ++i) {
+    const float f = lf[i], in = li[i];
+    const float m_new = fmaxf(f + m, in);
+    const float a = expf(f + m - m_new), b = expf(in - m_new);
+    m = m_new;
+    __syncwarp();
+    if (lane == 0) { lf[i] = a; li[i] = b; em[i] = expf(-m); }
+  }
+}
+
+template <typename L, int CP, int SPLIT>
+__device__ __forceinline__ void memory_tokens_n(float (&S)[CP][L::DP], float (&nn)[L::DP], const float* qs, const float* ks, const float* vs,
+                                                const float* li, const float* lf, const float* em, float* os, int nt, int part,
+                                                int col0, int dvp) {
+  constexpr int DP = L::DP, ROW = L::ROW;
+  float4 kc[DP / 4], qc[DP / 4];
+  scan_fetch<DP>(kc, ks + part * L::STRIDE);
+  scan_fetch<DP>(qc, qs + part * L::STRIDE);
+  for (int i = 0; i < nt; ++i) {
+    float4 kn[DP / 4], qn[DP / 4];
+    const int nx = min(i + 1, nt - 1) * ROW + part * L::STRIDE;
+    scan_fetch<DP>(kn, ks + nx); scan_fetch<DP>(qn, qs + nx);
+    const float a = lf[i], b = li[i];
+    float bv[CP], o[CP][2], nq0 = 0.f, nq1 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CP; ++c) { bv[c] = b * vs[i * dvp + col0 + c]; o[c][0] = o[c][1] = 0.f; }
+#pragma unroll
+    for (int d = 0; d < DP / 4; ++d) {
+      const float4 kk = kc[d], qq = qc[d];
+      nn[4 * d] = fmaf(b, kk.x, a * nn[4 * d]); nn[4 * d + 1] = fmaf(b, kk.y, a * nn[4 * d + 1]);
+      nn[4 * d + 2] = fmaf(b, kk.z, a * nn[4 * d + 2]); nn[4 * d + 3] = fmaf(b, kk.w, a * nn[4 * d + 3]);
+      nq0 = fmaf(nn[4 * d], qq.x, nq0); nq1 = fmaf(nn[4 * d + 1], qq.y, nq1);
+      nq0 = fmaf(nn[4 * d + 2], qq.z, nq0); nq1 = fmaf(nn[4 * d + 3], qq.w, nq1);
+#pragma unroll
+      for (int c = 0; c < CP; ++c) {
+        S[c][4 * d] = fmaf(bv[c], kk.x, a * S[c][4 * d]); S[c][4 * d + 1] = fmaf(bv[c], kk.y, a * S[c][4 * d + 1]);
+        S[c][4 * d + 2] = fmaf(bv[c], kk.z, a * S[c][4 * d + 2]); S[c][4 * d + 3] = fmaf(bv[c], kk.w, a * S[c][4 * d + 3]);
+        o[c][0] = fmaf(S[c][4 * d], qq.x, o[c][0]); o[c][1] = fmaf(S[c][4 * d + 1], qq.y, o[c][1]);
+        o[c][0] = fmaf(S[c][4 * d + 2], qq.z, o[c][0]); o[c][1] = fmaf(S[c][4 * d + 3], qq.w, o[c][1]);
+      }
+    }
+    // one division per token, not one per column: the columns take the reciprocal (a last-bit difference from y / den)
+    const float inv = 1.0f / (fmaxf(fabsf(split_sum<SPLIT>(nq0 + nq1)), em[i]) + 1e-6f);
+#pragma unroll
+    for (int c = 0; c < CP; ++c) {
+      const float y = split_sum<SPLIT>(o[c][0] + o[c][1]);
+      if (part == 0) os[i * dvp + col0 + c] = y * inv;
+    }
+#pragma unroll
+    for (int d = 0; d < DP / 4; ++d) { kc[d] = kn[d]; qc[d] = qn[d]; }
+  }
+}
+
 // The matrix memory for long prompts: chunks of 16 tokens staged by asynchronous copies, two deep (what is computed while
 // staging is little here: q times 1 / sqrt(dk) and the two log gates of a token, done when a chunk has landed).
 template <int DK, int CT, int SPLIT, int CP>
@@ -646,15 +703,11 @@ __global__ void __launch_bounds__(512) matrix_memory_scan_pre_kernel(MemoryIn P,
   float* m_state = slot + (size_t)P.heads * dk * dv + (size_t)P.heads * dk + h;
   float S[CP][DP];
   scan_state_load<CP, DP>(S, S_state, d0, colbase + col0, dk, dv);
-  constexpr int NJ = (DK + 31) / 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  float nreg[NJ];
-  float m = 0.f;
-  if (warp == 0) {
+  float nn[DP];                        // this thread's part of the normaliser
 #pragma unroll
-    for (int j = 0; j < NJ; ++j) nreg[j] = (lane + 32 * j < dk) ? n_state[lane + 32 * j] : 0.f;
-    m = *m_state;
-  }
+  for (int d = 0; d < DP; ++d) nn[d] = d0 + d < dk ? n_state[d0 + d] : 0.f;
+  float m = warp == 0 ? *m_state : 0.f;
   const float q_scale = 1.0f / sqrtf((float)dk);
   const float bi = co_load_any(P.bias_i, P.bias_dtype, h), bf = co_load_any(P.bias_f, P.bias_dtype, h);
   for (int e = threadIdx.x; e < 2 * STAGE; e += blockDim.x) smem[e] = 0.f;      // the padding of both stages, once
@@ -701,22 +754,22 @@ __global__ void __launch_bounds__(512) matrix_memory_scan_pre_kernel(MemoryIn P,
       lf[threadIdx.x] = -rc_softplus(-z);
     }
     __syncthreads();
-    if (warp == 0) memory_scalars<L, NJ>(nreg, m, qs, ks, li, lf, den, nt, lane);
+    if (warp == 0) memory_factors(m, li, lf, den, nt, lane);
     __syncthreads();
-    memory_tokens<L, CP, SPLIT>(S, qs, ks, vs, li, lf, den, os, nt, part, col0, dvp);
+    memory_tokens_n<L, CP, SPLIT>(S, nn, qs, ks, vs, li, lf, den, os, nt, part, col0, dvp);
     __syncthreads();
     if (E.raw) raw_out_chunk(E, os, dvp, dv, colbase, nt, row0, h);
     else head_out_chunk(E, os, dvp, dv, nt, row0, h);
     __syncthreads();
   }
   scan_state_store<CP, DP>(S, S_state, d0, colbase + col0, dk, dv);
-  if (warp == 0 && blockIdx.z == 0) {
+  if (blockIdx.z == 0 && threadIdx.x < SPLIT) {      // the first group of lanes holds the whole of n between them
     float* n_to = E.nm_next ? E.nm_next + ((size_t)r * P.heads + h) * (dk + 1) : n_state;
     float* m_to = E.nm_next ? n_to + dk : m_state;
 #pragma unroll
-    for (int j = 0; j < NJ; ++j)
-      if (lane + 32 * j < dk) n_to[lane + 32 * j] = nreg[j];
-    if (lane == 0) *m_to = m;
+    for (int d = 0; d < DP; ++d)
+      if (d0 + d < dk) n_to[d0 + d] = nn[d];
+    if (threadIdx.x == 0) *m_to = m;
   }
 }
 
