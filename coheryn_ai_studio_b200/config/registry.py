@@ -15,6 +15,7 @@ from typing import Any, Callable, Dict, Optional, Tuple
 from .qwen2 import (ConfigError, Qwen2Config, qwen2_config_from_gguf, qwen2_gguf_metadata, qwen2_gguf_name_of,
                     qwen2_gguf_tensor_name, qwen2_model_spec, read_config_json)
 from .kapudra import KapudraConfig, kapudra_model_spec
+from .tutunex import TutunexConfig, tutunex_model_spec
 from .spec import ModelSpec
 
 
@@ -186,3 +187,4 @@ register_architecture("Qwen2ForCausalLM", Qwen2Config.from_dict, qwen2_model_spe
                                     qwen2_gguf_metadata, qwen2_gguf_name_of),
                       adapter_id="qwen2-b200-v1")
 register_architecture("Kapudra", KapudraConfig.from_dict, kapudra_model_spec, adapter_id="kapudra-b200-v1")
+register_architecture("Tutunex", TutunexConfig.from_dict, tutunex_model_spec, adapter_id="tutunex-b200-v1")

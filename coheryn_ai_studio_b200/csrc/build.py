@@ -32,6 +32,7 @@ CORE_SOURCES = ["runtime.cu", "elementwise.cu", "gemm_simt.cu", "attention_simpl
                 "sampling.cu", "gemm_bf16_small.cu", "gemm_tc.cu", "gemm_tc_few.cu", "seeded_fill.cu", "selftest.cu",
                 "block_runner.cu"]
 RECURRENT_SOURCES = ["recurrent.cu", "runtime.cu"]
+VARIANT_SOURCES = ["attention_variants.cu", "runtime.cu"]
 HEADERS = ["common.cuh"]
 
 
@@ -241,9 +242,16 @@ def recurrent_library() -> ctypes.CDLL:
     return load_library("recurrent", RECURRENT_SOURCES)
 
 
+def variants_library() -> ctypes.CDLL:
+    """Attention with several score maps per head, a mask by chunks, a sink, a normalised output; queries and keys
+    normalised per head and rotated by computed angles.  Compiled when a model with such a mixer is first run."""
+    return load_library("variants", VARIANT_SOURCES)
+
+
 def build_all(head_dims: Sequence[int] = (16, 32, 64, 128)) -> List[str]:
     """Compile everything ahead of time (no GPU needed)."""
-    paths = [build_host_library(), build_library("core", CORE_SOURCES), build_library("recurrent", RECURRENT_SOURCES)]
+    paths = [build_host_library(), build_library("core", CORE_SOURCES), build_library("recurrent", RECURRENT_SOURCES),
+             build_library("variants", VARIANT_SOURCES)]
     for hd in head_dims:
         paths.append(build_library(f"attn_hd{hd}", ["attention_bf16.cu", "attention_tc.cu", "runtime.cu"],
                                    {"CO_HEAD_DIM": hd}))

@@ -142,6 +142,23 @@ __device__ __forceinline__ float co_gate_act(int code, float g) {
   return code == 2 ? co_gelu_tanh(g) : __fdividef(g, 1.0f + __expf(-g));
 }
 
+// The epilogue word of a gated product: the low byte is the activation's code, the upper 24 bits are a constant of the
+// activation as the upper 24 bits of its float32 form (sign, exponent, 15 bits of mantissa; zero for codes 1 and 2).
+// Code 3: with the constant c, g <- min(g, c), u <- clamp(u, -c, c), result g sigmoid(1.702 g) (u + 1).
+#define CO_GATE_CLAMPED_SWISH 3
+__device__ __forceinline__ float co_gate_const(int e) { return __int_as_float(e & 0xffffff00); }
+__device__ __forceinline__ float co_gated(int e, float g, float u) {
+  if ((e & 0xff) == CO_GATE_CLAMPED_SWISH) {
+    const float c = co_gate_const(e);
+    g = fminf(g, c);
+    u = fminf(fmaxf(u, -c), c);
+    return __fdividef(g, 1.0f + __expf(-1.702f * g)) * (u + 1.0f);
+  }
+  return co_gate_act(e, g) * u;
+}
+// Whether an epilogue word is one the gated epilogues know.
+inline bool co_epilogue_known(int e) { return e >= 0 && ((e & 0xff) <= 2 ? e <= 2 : (e & 0xff) == CO_GATE_CLAMPED_SWISH); }
+
 __device__ __forceinline__ float co_warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

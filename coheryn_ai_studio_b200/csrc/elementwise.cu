@@ -560,34 +560,137 @@ CO_EXPORT int coheryn_add_parts_rmsnorm(float* resid, const float* parts, int sp
 // silu(g) = g / (1 + exp(-g)) in float32.
 // ---------------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int I, size_t total, int code) {
+__global__ void silu_mul_kernel(const T* __restrict__ in, T* __restrict__ out, int I, size_t total, int code, float param,
+                                long ldo) {
   co_pdl_launch_dependents();
   co_pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (size_t)gridDim.x * blockDim.x) {
     const size_t m = i / I, j = i % I;
-    const float g = co_to_float(in[m * 2 * I + 2 * j]);
-    const float u = co_to_float(in[m * 2 * I + 2 * j + 1]);
-    out[i] = co_from_float<T>((code == 2 ? co_gelu_tanh(g) : g / (1.0f + expf(-g))) * u);
+    float g = co_to_float(in[m * 2 * I + 2 * j]);
+    float u = co_to_float(in[m * 2 * I + 2 * j + 1]);
+    float r;
+    if (code == CO_GATE_CLAMPED_SWISH) {     // the constant in full float32 here
+      g = fminf(g, param);
+      u = fminf(fmaxf(u, -param), param);
+      r = g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+    } else {
+      r = (code == 2 ? co_gelu_tanh(g) : g / (1.0f + expf(-g))) * u;
+    }
+    out[m * ldo + j] = co_from_float<T>(r);
   }
 }
 
-CO_EXPORT int coheryn_act_mul(const void* in, void* out, int dtype, int M, int I, int code, cudaStream_t stream);
+CO_EXPORT int coheryn_act_mul_ex(const void* in, void* out, int dtype, int M, int I, int code, float param, long ldo,
+                                 cudaStream_t stream);
 CO_EXPORT int coheryn_silu_mul(const void* in, void* out, int dtype, int M, int I, cudaStream_t stream) {
-  return coheryn_act_mul(in, out, dtype, M, I, 1, stream);
+  return coheryn_act_mul_ex(in, out, dtype, M, I, 1, 0.f, I, stream);
+}
+CO_EXPORT int coheryn_act_mul(const void* in, void* out, int dtype, int M, int I, int code, cudaStream_t stream) {
+  return coheryn_act_mul_ex(in, out, dtype, M, I, code, 0.f, I, stream);
 }
 
-// code: 1 SiLU, 2 the tanh form of GELU (the codes of the products' gated epilogues).
-CO_EXPORT int coheryn_act_mul(const void* in, void* out, int dtype, int M, int I, int code, cudaStream_t stream) {
-  if (code != 1 && code != 2) CO_FAIL("act_mul: unknown activation code %d", code);
+// code: 1 SiLU, 2 the tanh form of GELU, 3 the clamped form with its constant `param` (the codes of the products' gated
+// epilogues).  `ldo`: elements between the rows of out.
+CO_EXPORT int coheryn_act_mul_ex(const void* in, void* out, int dtype, int M, int I, int code, float param, long ldo,
+                                 cudaStream_t stream) {
+  if (code < 1 || code > 3) CO_FAIL("act_mul: unknown activation code %d", code);
+  if (code == 3 && !(param > 0.f)) CO_FAIL("act_mul: the clamp of activation 3 must be positive");
   const size_t total = (size_t)M * I;
   if (total == 0) return 0;
   const int threads = 256;
   const int blocks = (int)((total + threads - 1) / threads < 148 * 16 ? (total + threads - 1) / threads : 148 * 16);
-  if (dtype == CO_F32) co_launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (float*)out, I, total, code);
-  else if (dtype == CO_BF16) co_launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, I, total, code);
+  if (dtype == CO_F32) co_launch(silu_mul_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (const float*)in, (float*)out, I, total, code, param, ldo);
+  else if (dtype == CO_BF16) co_launch(silu_mul_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, I, total, code, param, ldo);
   else CO_FAIL("silu_mul: unknown dtype %d", dtype);
   CO_CHECK_LAUNCH("silu_mul");
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------
+// A residual add whose summand is normalised first, fused with the norm that reads the sum:
+//   y = sum_p parts[p]                                     (inner == 0), or
+//   y = coef * sum_p parts[p] / rms(parts[p]) * inner_w[p] (inner == 1: each part normalised by itself, a weight each)
+//   x = resid + y / rms(y) * post_w;   resid = x (update);   out = x / rms(x) * w  (when w is given)
+// rms(z) = sqrt(mean(z^2) + eps).  One CTA per row; the row's y and x live in shared memory ([2][H] floats).
+// With `rows` the CTA r reads row rows[r] and the residual stays as it is.
+// ---------------------------------------------------------------------------------
+template <typename TO>
+__global__ void __launch_bounds__(256)
+add_normed_rmsnorm_kernel(float* __restrict__ resid, const float* __restrict__ parts, int n_parts, size_t part_stride, long ldp,
+                          const void* __restrict__ inner_w, int inner_dtype, float coef, const void* __restrict__ post_w,
+                          int post_dtype, const int* __restrict__ rows, const void* __restrict__ w, int w_dtype, float eps,
+                          TO* __restrict__ out, int H, int update) {
+  extern __shared__ __align__(16) float row_s[];
+  __shared__ float scratch[33];
+  float* ys = row_s;
+  co_pdl_launch_dependents();
+  co_pdl_wait();
+  const int r = blockIdx.x;
+  const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+  const float invH = 1.0f / (float)H;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) ys[j] = 0.f;
+  for (int p = 0; p < n_parts; ++p) {
+    const float* d = parts + p * part_stride + src * ldp;
+    float scale = 1.f;
+    if (inner_w) {
+      float ss = 0.f;
+      for (int j = threadIdx.x; j < H; j += blockDim.x) ss = fmaf(d[j], d[j], ss);
+      ss = co_block_sum(ss, scratch);
+      scale = 1.0f / sqrtf(ss * invH + eps);
+    }
+    for (int j = threadIdx.x; j < H; j += blockDim.x)    // a thread touches its own elements of ys only
+      ys[j] += inner_w ? (d[j] * scale) * co_load_any(inner_w, inner_dtype, (size_t)p * H + j) : d[j];
+  }
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    const float y = inner_w ? ys[j] * coef : ys[j];
+    ys[j] = y;
+    ss = fmaf(y, y, ss);
+  }
+  ss = co_block_sum(ss, scratch);
+  const float ps = 1.0f / sqrtf(ss * invH + eps);
+  float* x = resid + src * H;
+  float sx = 0.f;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) {
+    const float v = x[j] + (ys[j] * ps) * co_load_any(post_w, post_dtype, j);
+    ys[j] = v;
+    if (update) x[j] = v;
+    sx = fmaf(v, v, sx);
+  }
+  if (!w) return;
+  sx = co_block_sum(sx, scratch);
+  const float xs = 1.0f / sqrtf(sx * invH + eps);
+  TO* o = out + (size_t)r * H;
+  for (int j = threadIdx.x; j < H; j += blockDim.x) o[j] = co_from_float<TO>((ys[j] * xs) * co_load_any(w, w_dtype, j));
+}
+
+// parts: float32 [n_parts][rows][H] (`part_stride` elements between parts, `ldp` between rows).  inner_w: [n_parts][H] or
+// null.  w and out may be null: the residual is only updated.
+CO_EXPORT int coheryn_add_normed_rmsnorm(float* resid, const float* parts, int n_parts, long part_stride, long ldp,
+                                         const void* inner_w, int inner_dtype, float coef, const void* post_w, int post_dtype,
+                                         const int* rows, const void* w, int w_dtype, float eps, void* out, int out_dtype,
+                                         int n_rows, int H, int update, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (n_parts < 1 || !parts || !post_w) CO_FAIL("add_normed_rmsnorm: %d parts", n_parts);
+  if (rows && update) CO_FAIL("add_normed_rmsnorm: cannot update the residual through a row gather");
+  if ((w == nullptr) != (out == nullptr)) CO_FAIL("add_normed_rmsnorm: a weight and an output go together");
+  const size_t smem = (size_t)H * sizeof(float);
+  const int threads = H >= 1024 ? 256 : 128;
+  if (out_dtype == CO_BF16) {
+    auto kern = add_normed_rmsnorm_kernel<__nv_bfloat16>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    co_launch(kern, dim3(n_rows), dim3(threads), smem, stream, resid, parts, n_parts, (size_t)part_stride, ldp, inner_w,
+              inner_dtype, coef, post_w, post_dtype, rows, w, w_dtype, eps, (__nv_bfloat16*)out, H, update);
+  } else if (out_dtype == CO_F32) {
+    auto kern = add_normed_rmsnorm_kernel<float>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    co_launch(kern, dim3(n_rows), dim3(threads), smem, stream, resid, parts, n_parts, (size_t)part_stride, ldp, inner_w,
+              inner_dtype, coef, post_w, post_dtype, rows, w, w_dtype, eps, (float*)out, H, update);
+  } else {
+    CO_FAIL("add_normed_rmsnorm: unknown output dtype %d", out_dtype);
+  }
+  CO_CHECK_LAUNCH("add_normed_rmsnorm");
   return 0;
 }
 

@@ -148,7 +148,8 @@ gemm_small_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
     }
     if (epilogue != 0) {
       // rows (n, n+1) = (gate_j, up_j), j = n / 2
-      const float r = (epilogue == EPI_GATED_GELU_TANH ? co_gelu_tanh(v0) : v0 / (1.0f + __expf(-v0))) * v1;
+      const float r = (epilogue & 0xff) == CO_GATE_CLAMPED_SWISH ? co_gated(epilogue, v0, v1)
+                      : (epilogue == EPI_GATED_GELU_TANH ? co_gelu_tanh(v0) : v0 / (1.0f + __expf(-v0))) * v1;
       const size_t o = (size_t)m * ldo + (n >> 1);
       if (out_dtype == CO_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(r);
       else ((float*)out)[o] = r;
@@ -322,7 +323,7 @@ CO_EXPORT int coheryn_gemm_bf16_small(const void* x, const void* w, const void* 
   if (K <= 0 || (K & 7) || (ldx & 7)) CO_FAIL("gemm_bf16_small: K = %d and the row stride %ld must be multiples of 8", K, ldx);
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_small: operands must be 16-byte aligned");
   if (epilogue != 0 && (N & 1)) CO_FAIL("gemm_bf16_small: gated epilogue needs an even number of rows");
-  if (epilogue < 0 || epilogue > EPI_GATED_GELU_TANH) CO_FAIL("gemm_bf16_small: unknown epilogue %d", epilogue);
+  if (!co_epilogue_known(epilogue)) CO_FAIL("gemm_bf16_small: unknown epilogue %d", epilogue);
   // Rows per CTA: as many as keep at least ~2 CTAs per SM (148 SMs); more rows per CTA
   // mean fewer re-reads of x through L2.  The warps of a CTA split K (a function of K
   // alone, so the order of summation never depends on M or N).

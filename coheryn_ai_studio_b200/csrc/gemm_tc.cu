@@ -52,8 +52,8 @@ __device__ __forceinline__ void store_chunk_tma(unsigned tmem_chunk, const float
       for (int j = 0; j < 16; j += 2) {
         const float g0 = __uint_as_float(r[2 * j]), u0 = __uint_as_float(r[2 * j + 1]);
         const float g1 = __uint_as_float(r[2 * j + 2]), u1 = __uint_as_float(r[2 * j + 3]);
-        h[q * 8 + (j >> 1)] = __floats2bfloat162_rn(co_gate_act(gated, g0) * u0,
-                                                    co_gate_act(gated, g1) * u1);
+        h[q * 8 + (j >> 1)] = __floats2bfloat162_rn(co_gated(gated, g0, u0),
+                                                    co_gated(gated, g1, u1));
       }
     }
   } else {
@@ -211,7 +211,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
-            v[j] = co_gate_act(epilogue, g) * u;
+            v[j] = co_gated(epilogue, g, u);
           }
           const int n_out = N >> 1;
           if (out_dtype == CO_BF16) {
@@ -283,7 +283,7 @@ __device__ __forceinline__ void store_piece(const unsigned (&r)[32], int row, in
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
       const float g = __uint_as_float(r[2 * j]), u = __uint_as_float(r[2 * j + 1]);
-      v[j] = co_gate_act(epilogue, g) * u;
+      v[j] = co_gated(epilogue, g, u);
     }
     if (out_dtype == CO_BF16) {
       __nv_bfloat16* p = (__nv_bfloat16*)out + (size_t)row * ldo + oc;
@@ -352,7 +352,7 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, int spli
       if (has1) v1 += p[1];
     }
     if (epilogue != EPI_PLAIN) {
-      const float r = co_gate_act(epilogue, v0) * v1;
+      const float r = co_gated(epilogue, v0, v1);
       const size_t o = (size_t)m * ldo + (n >> 1);
       if (out_dtype == CO_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(r);
       else ((float*)out)[o] = r;
@@ -920,7 +920,7 @@ CO_EXPORT int coheryn_gemm_bf16_tc(const void* x, const void* w, const void* bia
   if (K <= 0 || (K & 7) || (ldx & 7)) CO_FAIL("gemm_bf16_tc: K = %d and the row stride %ld must be multiples of 8", K, ldx);
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_tc: operands must be 16-byte aligned");
   if (epilogue != 0 && (N & 1)) CO_FAIL("gemm_bf16_tc: gated epilogue needs an even number of rows");
-  if (epilogue < 0 || epilogue > 2) CO_FAIL("gemm_bf16_tc: unknown epilogue %d", epilogue);
+  if (!co_epilogue_known(epilogue)) CO_FAIL("gemm_bf16_tc: unknown epilogue %d", epilogue);
   if (status && pair_suits(M, N))
     return coheryn_gemm_bf16_tc_pair(x, w, bias, bias_dtype, out, out_dtype, M, N, K, ldx, ldo, epilogue, status, stream);
   const int bn = tile_width(M, N);
@@ -986,7 +986,7 @@ CO_EXPORT int coheryn_gemm_bf16_tc_pair(const void* x, const void* w, const void
   if (K <= 0 || (K & 7) || (ldx & 7)) CO_FAIL("gemm_bf16_tc_pair: K = %d and the row stride %ld must be multiples of 8", K, ldx);
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_tc_pair: operands must be 16-byte aligned");
   if (epilogue != 0 && (N & 1)) CO_FAIL("gemm_bf16_tc_pair: gated epilogue needs an even number of rows");
-  if (epilogue < 0 || epilogue > 2) CO_FAIL("gemm_bf16_tc_pair: unknown epilogue %d", epilogue);
+  if (!co_epilogue_known(epilogue)) CO_FAIL("gemm_bf16_tc_pair: unknown epilogue %d", epilogue);
   if (!status) CO_FAIL("gemm_bf16_tc_pair: a status word is required");
   CUtensorMap mx, mw;
   if (!make_map(&mx, x, M, K, ldx, BM) || !make_map(&mw, w, N, K, K, 128))

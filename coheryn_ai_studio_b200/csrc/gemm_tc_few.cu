@@ -133,7 +133,7 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const float g = __uint_as_float(r[j]);
             const float other = __shfl_xor_sync(0xffffffffu, g, 1);
             if (c0 + j < M && !(lane & 1) && n + 1 < N && (n >> 1) < n_out) {
-              const float y = co_gate_act(epilogue, g) * other;
+              const float y = co_gated(epilogue, g, other);
               const size_t o = (size_t)(c0 + j) * ldo + (n >> 1);
               if (out_dtype == CO_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(y);
               else ((float*)out)[o] = y;
@@ -213,7 +213,7 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (int j = 0; j < BT; ++j) {
           const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
           if (j < M && !(lane & 1) && n + 1 < N) {
-            const float r = co_gate_act(epilogue, v[j]) * other;
+            const float r = co_gated(epilogue, v[j], other);
             const size_t o = (size_t)j * ldo + (n >> 1);
             if ((n >> 1) < n_out) {
               if (out_dtype == CO_BF16) ((__nv_bfloat16*)out)[o] = __float2bfloat16_rn(r);
@@ -312,7 +312,7 @@ CO_EXPORT int coheryn_gemm_bf16_tc_few(const void* x, const void* w, const void*
   if (K <= 0 || (K & 7) || (ldx & 7)) CO_FAIL("gemm_bf16_tc_few: K = %d and the row stride %ld must be multiples of 8", K, ldx);
   if (((uintptr_t)x & 15) || ((uintptr_t)w & 15)) CO_FAIL("gemm_bf16_tc_few: operands must be 16-byte aligned");
   if (epilogue != 0 && (N & 1)) CO_FAIL("gemm_bf16_tc_few: gated epilogue needs an even number of rows");
-  if (epilogue < 0 || epilogue > 2) CO_FAIL("gemm_bf16_tc_few: unknown epilogue %d", epilogue);
+  if (!co_epilogue_known(epilogue)) CO_FAIL("gemm_bf16_tc_few: unknown epilogue %d", epilogue);
   const int splits = few_splits(N, K);
   if (defer && (epilogue != 0 || out_dtype != CO_F32)) CO_FAIL("gemm_bf16_tc_few: deferred splits are float32 and take no gate");
   if (splits > 1 && !defer && (!workspace || workspace_floats < coheryn_gemm_tc_few_workspace_floats(M, N, K)))

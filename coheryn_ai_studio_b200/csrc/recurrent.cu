@@ -96,6 +96,7 @@ struct HeadOut {
   // head) wait until every CTA of the head has read the old ones ([B][heads][dk + 1]).
   float* raw; long ldr;
   float* nm_next;
+  int gate_act;                                // what the gate's pre-activation passes: 0 sigmoid, 1 SiLU
 };
 
 __device__ __forceinline__ void head_out_chunk(const HeadOut& E, const float* os, int dvp, int dv, int nt, int row0, int h) {
@@ -109,7 +110,8 @@ __device__ __forceinline__ void head_out_chunk(const HeadOut& E, const float* os
 #pragma unroll 4
     for (int c = lane; c < dv; c += 32) {
       const float w = co_load_any(E.weight, E.weight_dtype, (size_t)h * E.weight_stride + c);
-      const float g = rc_sigmoid(E.gate[row * E.ldg + (size_t)h * dv + c]);
+      const float z = E.gate[row * E.ldg + (size_t)h * dv + c];
+      const float g = E.gate_act == 1 ? z * rc_sigmoid(z) : rc_sigmoid(z);
       rc_store(E.out, E.out_dtype, row * E.ldo + (size_t)h * dv + c, os[i * dvp + c] * inv * w * g * E.out_scale);
     }
   }
@@ -224,12 +226,13 @@ __device__ __forceinline__ float split_sum(float v) {
 struct DeltaIn {
   const float* q; const float* k; const float* v; long ld_qkv;   // after convolution and SiLU: [T, kv_heads*dk], .., [T, heads*dv]
   const float* beta; long ld_beta;                               // pre-activation of beta [T, heads]
-  const float* step; long ld_step;                               // pre-activation of the step size [T, heads*dk] (bias not added)
-  const void* step_bias; int step_bias_dtype;                    // [heads*dk]
+  const float* step; long ld_step;                               // pre-activation of the step size [T, heads*dc] (bias not added)
+  const void* step_bias; int step_bias_dtype;                    // [heads*dc]; dc = decay_channels
   const void* rate_log; int rate_log_dtype;                      // [heads]: decay = exp(-exp(rate_log) * softplus(step + bias))
   float* state; long state_stride;                               // per slot: S [heads, dk, dv]
   const int* cu_q; const int* state_slots;
   int heads, kv_heads, dk, dv;
+  int decay_channels;                                            // dk: a decay per head and key channel; 1: one per head
 };
 
 // The tokens of a staged chunk, one after the other, for the thread's part of S (see ScanShape).
@@ -323,7 +326,8 @@ __global__ void __launch_bounds__(512) gated_delta_scan_kernel(DeltaIn P, HeadOu
       if (d < dk) {
         qv = P.q[row * P.ld_qkv + (size_t)g * dk + d];
         kv = P.k[row * P.ld_qkv + (size_t)g * dk + d];
-        const float z = P.step[row * P.ld_step + (size_t)h * dk + d] + co_load_any(P.step_bias, P.step_bias_dtype, (size_t)h * dk + d);
+        const size_t sc = P.decay_channels == 1 ? (size_t)h : (size_t)h * dk + d;
+        const float z = P.step[row * P.ld_step + sc] + co_load_any(P.step_bias, P.step_bias_dtype, sc);
         gv = expf(-rate * rc_softplus(z));
       }
       const int o = i * ROW + L::at(d);
@@ -390,7 +394,8 @@ __global__ void __launch_bounds__(128) delta_prepare_kernel(DeltaIn P, float* __
   }
   for (int e = threadIdx.x; e < H * dk; e += blockDim.x) {
     const float rate = expf(co_load_any(P.rate_log, P.rate_log_dtype, e / dk));
-    const float z = P.step[t * P.ld_step + e] + co_load_any(P.step_bias, P.step_bias_dtype, e);
+    const size_t sc = P.decay_channels == 1 ? (size_t)(e / dk) : (size_t)e;
+    const float z = P.step[t * P.ld_step + sc] + co_load_any(P.step_bias, P.step_bias_dtype, sc);
     out[(size_t)2 * G * dk + e] = expf(-rate * rc_softplus(z));
   }
   for (int e = threadIdx.x; e < H; e += blockDim.x) out[(size_t)(2 * G + H) * dk + e] = rc_sigmoid(P.beta[t * P.ld_beta + e]);
@@ -882,17 +887,20 @@ CO_EXPORT int coheryn_gated_delta_scan(
     long ld_step, const void* step_bias, int step_bias_dtype, const void* rate_log, int rate_log_dtype, float* state,
     long state_stride, const int* cu_q, const int* state_slots, int B, int heads, int kv_heads, int dk, int dv, void* out,
     int out_dtype, long ldo, const void* weight, int weight_dtype, int weight_stride, const float* gate, long ldg, float eps,
-    float out_scale, int total_tokens, float* scratch, long scratch_floats, cudaStream_t stream) {
+    float out_scale, int total_tokens, float* scratch, long scratch_floats, int decay_channels, int gate_act,
+    cudaStream_t stream) {
   if (B <= 0) return 0;
   if (!scan_shape_ok("gated_delta_scan", heads, dk, dv)) return 1;
+  if (decay_channels != 1 && decay_channels != dk) CO_FAIL("gated_delta_scan: a decay per head (1) or per key channel (%d), not %d", dk, decay_channels);
+  if (gate_act != 0 && gate_act != 1) CO_FAIL("gated_delta_scan: unknown gate activation %d", gate_act);
   const long ld_prep = (long)2 * kv_heads * dk + (long)heads * dk + heads;     // per token: q, k, decays, beta
   const int slices = scan_slices(B, heads, dv, total_tokens, scratch, scratch_floats, (long)total_tokens * ld_prep);
   float* prep = slices > 1 ? scratch + (long)total_tokens * heads * dv : nullptr;
   if (kv_heads < 1 || heads % kv_heads) CO_FAIL("gated_delta_scan: %d heads do not group over %d q/k heads", heads, kv_heads);
   DeltaIn P{q, k, v, ld_qkv, beta, ld_beta, step, ld_step, step_bias, step_bias_dtype, rate_log, rate_log_dtype, state,
-            state_stride, cu_q, state_slots, heads, kv_heads, dk, dv};
+            state_stride, cu_q, state_slots, heads, kv_heads, dk, dv, decay_channels};
   HeadOut E{out, out_dtype, ldo, weight, weight_dtype, weight_stride, gate, ldg, eps, out_scale,
-            slices > 1 ? scratch : nullptr, (long)heads * dv, nullptr};
+            slices > 1 ? scratch : nullptr, (long)heads * dv, nullptr, gate_act};
   if (slices > 1) {
     co_launch(delta_prepare_kernel, dim3(total_tokens), dim3(128), 0, stream, P, prep, ld_prep);
     CO_CHECK_LAUNCH("delta_prepare");

@@ -55,7 +55,7 @@ def launch_count() -> int:
 def total_launch_count() -> int:
     """Kernel launches made through every library of this package that is loaded."""
     n = launch_count()
-    for lib in list(_attn_libs.values()) + ([_recurrent] if _recurrent is not None else []):
+    for lib in list(_attn_libs.values()) + [l for l in (_recurrent, _variants) if l is not None]:
         n += int(lib.coheryn_launch_count())
     return n
 
@@ -215,16 +215,50 @@ def add_rmsnorm(resid: torch.Tensor, delta: Optional[torch.Tensor], weight: torc
         c_int(H), c_int(1 if (update and delta is not None) else 0), _stream()))
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, code: int = 1) -> None:
-    """out[m, j] = act(gate_up[m, 2j]) * gate_up[m, 2j + 1] (gate and up interleaved); ``code`` names the
-    activation as the gated epilogues do (``GATED_ACTIVATIONS``; 1 = SiLU)."""
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, code: int = 1, param: float = 0.0) -> None:
+    """out[m, j] = act(gate_up[m, 2j], gate_up[m, 2j + 1]) (gate and up interleaved); ``code`` names the
+    activation as the gated epilogues do (``GATED_ACTIVATIONS``; 1 = SiLU), ``param`` is its constant where
+    it has one (in full float32 here).  The rows of ``out`` may be strided."""
     _dev(gate_up, out)
     M, I2 = gate_up.shape
     assert I2 % 2 == 0 and out.shape == (M, I2 // 2) and out.dtype == gate_up.dtype
-    assert gate_up.is_contiguous() and out.is_contiguous()
+    assert gate_up.is_contiguous() and out.stride(1) == 1
     lib = core()
-    _check(lib, lib.coheryn_act_mul(_ptr(gate_up), _ptr(out), c_int(_code(out)), c_int(M),
-                                    c_int(I2 // 2), c_int(code), _stream()))
+    _check(lib, lib.coheryn_act_mul_ex(_ptr(gate_up), _ptr(out), c_int(_code(out)), c_int(M), c_int(I2 // 2),
+                                       c_int(code & 0xff), c_float(param), c_long(out.stride(0)), _stream()))
+
+
+def add_normed_rmsnorm(resid: torch.Tensor, parts: torch.Tensor, inner_weights: Optional[torch.Tensor], coef: float,
+                       post_weight: torch.Tensor, weight: Optional[torch.Tensor], eps: float, out: Optional[torch.Tensor],
+                       rows: Optional[torch.Tensor] = None) -> None:
+    """A residual add whose summand is normalised first, fused with the norm that reads the sum.  ``parts`` float32
+    [P, n, H] (or [n, H]): y = sum of the parts, or with ``inner_weights`` [P, H] y = coef * sum_p parts[p] /
+    rms(parts[p]) * inner_weights[p]; x = resid + y / rms(y) * post_weight; resid = x (without ``rows``);
+    out = x / rms(x) * weight (when a weight and an output are given).  rms(z) = sqrt(mean(z^2) + eps).
+    With ``rows`` only those rows are read and the residual stays as it is."""
+    _dev(resid, parts, inner_weights, post_weight, weight, out, rows)
+    if parts.dim() == 2:
+        parts = parts.unsqueeze(0)
+    P, n_all, H = parts.shape
+    assert parts.dtype == torch.float32 and parts.stride(2) == 1 and resid.dtype == torch.float32 and resid.is_contiguous()
+    assert resid.shape[-1] == H and post_weight.shape == (H,) and post_weight.is_contiguous()
+    if inner_weights is not None:
+        assert inner_weights.shape == (P, H) and inner_weights.is_contiguous()
+    n = resid.shape[0]
+    if rows is not None:
+        _i32(rows, "rows")
+        n = rows.numel()
+    else:
+        assert n_all == n
+    if out is not None:
+        assert weight is not None and weight.shape == (H,) and out.is_contiguous() and out.shape == (n, H)
+    lib = core()
+    _check(lib, lib.coheryn_add_normed_rmsnorm(
+        _ptr(resid), _ptr(parts), c_int(P), c_long(parts.stride(0)), c_long(parts.stride(1)), _ptr(inner_weights),
+        c_int(_code(inner_weights) if inner_weights is not None else F32), c_float(coef), _ptr(post_weight),
+        c_int(_code(post_weight)), _ptr(rows), _ptr(weight if out is not None else None),
+        c_int(_code(weight) if weight is not None else F32), c_float(eps), _ptr(out),
+        c_int(_code(out) if out is not None else F32), c_int(n), c_int(H), c_int(0 if rows is not None else 1), _stream()))
 
 
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, cos_sin: torch.Tensor,
@@ -871,7 +905,9 @@ def attention_oproj(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
 # Activations of the gated epilogue, by the code that the kernels take as their ``gated`` argument
 # (0 means "no gate").  The gate is applied in float32 inside the product's epilogue; an activation
 # that is not built is refused here by name, before anything is launched.
-GATED_ACTIVATIONS = {"silu": 1, "gelu_tanh": 2}
+# "swish_clamped" has a constant c: g <- min(g, c), u <- clamp(u, -c, c), result g sigmoid(1.702 g) (u + 1).
+GATED_ACTIVATIONS = {"silu": 1, "gelu_tanh": 2, "swish_clamped": 3}
+GATED_WITH_CONSTANT = ("swish_clamped",)
 
 
 def gated_activation_code(activation: str) -> int:
@@ -882,12 +918,30 @@ def gated_activation_code(activation: str) -> int:
                           f"(built: {', '.join(sorted(GATED_ACTIVATIONS))})") from None
 
 
+def gated_epilogue_word(activation: str, param: Optional[float] = None) -> int:
+    """What the products take as their ``gated`` argument: the activation's code in the low byte and, for an
+    activation with a constant, the constant rounded to the upper 24 bits of its float32 form (15 bits of
+    mantissa, far below what a bfloat16 result can show; the unfused kernel takes it whole)."""
+    code = gated_activation_code(activation)
+    if activation not in GATED_WITH_CONSTANT:
+        return code
+    if param is None or not param > 0:
+        raise KernelError(f"activation {activation!r} needs a positive constant")
+    import struct
+    bits = struct.unpack("<I", struct.pack("<f", float(param)))[0]
+    bits = (bits + 0x80) & 0xffffff00
+    if bits >= 0x7f800000:
+        raise KernelError(f"the constant {param!r} of activation {activation!r} is out of range")
+    return bits | code
+
+
 def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, activation: str = "silu",
-                 out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 out: Optional[torch.Tensor] = None, param: Optional[float] = None) -> torch.Tensor:
     """act(x @ Wg.T) * (x @ Wu.T) for w_gate_up with INTERLEAVED rows (row 2j = gate_j,
     row 2j+1 = up_j), so that a gate/up pair lands in one thread of the epilogue.  ``out`` ([M, I] of x's dtype, rows
-    may be strided: a column slice of a wider buffer) receives the result when given."""
-    code = gated_activation_code(activation)
+    may be strided: a column slice of a wider buffer) receives the result when given.  ``param``: the constant of an
+    activation that has one."""
+    code = gated_epilogue_word(activation, param)
     M = x.shape[0]
     I = w_gate_up.shape[0] // 2
     if out is None:
@@ -907,12 +961,7 @@ def gated_linear(x: torch.Tensor, w_gate_up: torch.Tensor, activation: str = "si
         return out
     gu = torch.empty((M, 2 * I), dtype=x.dtype, device=x.device)
     gemm_simt(x, w_gate_up, None, gu)
-    if out.is_contiguous():
-        silu_mul(gu, out, code)
-    else:
-        tmp = torch.empty((M, I), dtype=x.dtype, device=x.device)
-        silu_mul(gu, tmp, code)
-        out.copy_(tmp)
+    silu_mul(gu, out, code, float(param or 0.0))
     return out
 
 
@@ -961,18 +1010,23 @@ def short_conv_silu(x: torch.Tensor, taps: torch.Tensor, state: torch.Tensor, st
 
 
 def gated_delta_scan(q, k, v, beta, step_pre, step_bias, rate_log, state, step, heads: int, kv_heads: int, dk: int, dv: int,
-                     out: torch.Tensor, norm_weight: torch.Tensor, gate: torch.Tensor, eps: float, out_scale: float = 1.0) -> None:
+                     out: torch.Tensor, norm_weight: torch.Tensor, gate: torch.Tensor, eps: float, out_scale: float = 1.0,
+                     decay_per_channel: bool = True, gate_activation: str = "sigmoid") -> None:
     """The gated delta rule over each request's run of tokens, continued from and left in ``state`` (float32 view
-    [slots, heads * dk * dv]), followed by the per-head RMS norm, its weight ([dv], shared by the heads) and the sigmoid of
-    ``gate``.  q, k [T, kv_heads*dk] and v [T, heads*dv]: float32 with ONE row stride (slices of one buffer); beta [T, heads],
-    step_pre [T, heads*dk], gate [T, heads*dv]: float32 pre-activations; out [T, heads*dv] in the compute dtype."""
+    [slots, heads * dk * dv]), followed by the per-head RMS norm, its weight ([dv], shared by the heads) and the sigmoid
+    (or, ``gate_activation = "silu"``, the SiLU) of ``gate``.  q, k [T, kv_heads*dk] and v [T, heads*dv]: float32 with ONE
+    row stride (slices of one buffer); beta [T, heads], step_pre [T, heads*dk] (``decay_per_channel``: a decay per head and
+    key channel) or [T, heads] (one per head), gate [T, heads*dv]: float32 pre-activations; out [T, heads*dv] in the
+    compute dtype."""
     _dev(q, k, v, beta, step_pre, step_bias, rate_log, state, out, norm_weight, gate)
     for t, name in ((q, "q"), (k, "k"), (v, "v"), (beta, "beta"), (step_pre, "step"), (state, "state"), (gate, "gate")):
         _f32(t, name)
     assert q.stride(0) == k.stride(0) == v.stride(0)
     assert q.shape[1] == kv_heads * dk and k.shape[1] == kv_heads * dk and v.shape[1] == heads * dv
-    assert beta.shape[1] == heads and step_pre.shape[1] == heads * dk and gate.shape[1] == heads * dv
-    assert step_bias.numel() == heads * dk and rate_log.numel() == heads and norm_weight.numel() == dv
+    dc = dk if decay_per_channel else 1
+    assert beta.shape[1] == heads and step_pre.shape[1] == heads * dc and gate.shape[1] == heads * dv
+    assert step_bias.numel() == heads * dc and rate_log.numel() == heads and norm_weight.numel() == dv
+    gate_code = {"sigmoid": 0, "silu": 1}[gate_activation]
     assert state.shape[1] == heads * dk * dv and out.shape == (q.shape[0], heads * dv) and out.stride(1) == 1
     lib = recurrent()
     scratch = _scan_scratch(q.shape[0], step.num_requests, heads, dv, q.shape[0] * (2 * kv_heads * dk + heads * dk + heads), q.device)
@@ -982,7 +1036,8 @@ def gated_delta_scan(q, k, v, beta, step_pre, step_bias, rate_log, state, step, 
         _ptr(state), c_long(state.stride(0)), _ptr(step.cu_q), _ptr(step.state_slots), c_int(step.num_requests),
         c_int(heads), c_int(kv_heads), c_int(dk), c_int(dv), _ptr(out), c_int(_code(out)), c_long(out.stride(0)),
         _ptr(norm_weight), c_int(_code(norm_weight)), c_int(0), _ptr(gate), c_long(gate.stride(0)), c_float(eps),
-        c_float(out_scale), c_int(q.shape[0]), _ptr(scratch), c_long(scratch.numel() if scratch is not None else 0), _stream()))
+        c_float(out_scale), c_int(q.shape[0]), _ptr(scratch), c_long(scratch.numel() if scratch is not None else 0),
+        c_int(dc), c_int(gate_code), _stream()))
 
 
 def matrix_memory_scan(q, k, v, gate_i, gate_f, bias_i, bias_f, cap: float, state, step, heads: int, dk: int, dv: int,
@@ -1038,3 +1093,82 @@ def qk_norm_kv_write(q, k, v, q_weight, k_weight, eps: float, slots, k_cache, v_
         c_int(_CODES[dtype]), c_long(q_out.stride(0)), _ptr(slots), _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(num_heads),
         c_int(num_kv_heads), c_int(dk), c_int(dv), c_int(page_size), c_float(v_scale), _stream()))
     return q_out
+
+
+# ------------------------------------------------------------------------------------
+# Attention with several score maps per head, a mask by chunks, a sink and a normalised output, and the kernel that
+# prepares its queries and keys (csrc/attention_variants.cu, a library of its own that is compiled when a model with
+# such a mixer is first run).
+_variants = None
+
+
+def variants():
+    global _variants
+    if _variants is None:
+        lib = build.variants_library()
+        lib.coheryn_last_error.restype = ctypes.c_char_p
+        lib.coheryn_launch_count.restype = ctypes.c_ulonglong
+        _variants = lib
+    return _variants
+
+
+def unit_norm_rope_kv_write(q, k, v, q_weight, k_weight, eps: float, positions, freq, rot: int, rot_scale: float, slots,
+                            k_cache, v_cache, q_units: int, k_units: int, num_kv_heads: int, dk: int, dv: int,
+                            page_size: int, dtype: torch.dtype) -> torch.Tensor:
+    """Queries and keys in units of ``dk`` channels (a head has one unit per score map): each unit divided by its root
+    mean square and multiplied by a weight [dk] shared by the units (skipped when ``q_weight`` is None), then its first
+    ``rot`` channels rotated by the token's position (pairs (i, i + rot/2); ``freq`` float32 [rot/2, 2] holds each pair's
+    frequency as a high and a low part, angle = position * frequency; cos and sin are multiplied by ``rot_scale``).  Keys
+    ([page, kv head, slot, k_units / kv heads * dk]) and values ([page, kv head, slot, dv]) go to the cache at ``slots``
+    (None: only the queries are made; k and v are not read).  q, k, v: float32 with one row stride.  Returns q
+    [T, q_units * dk] in ``dtype``."""
+    _dev(q, k, v, q_weight, k_weight, positions, freq, slots, k_cache, v_cache)
+    _f32(q, "q")
+    T = q.shape[0]
+    assert q.shape[1] == q_units * dk
+    if slots is not None:
+        _f32(k, "k"); _f32(v, "v"); _i32(slots, "slots")
+        assert q.stride(0) == k.stride(0) == v.stride(0)
+        assert k.shape[1] == k_units * dk and v.shape[1] == num_kv_heads * dv
+        assert k_cache.dtype == dtype and v_cache.dtype == dtype and k_cache.is_contiguous() and v_cache.is_contiguous()
+        assert tuple(k_cache.shape[1:]) == (num_kv_heads, page_size, k_units // num_kv_heads * dk)
+        assert tuple(v_cache.shape[1:]) == (num_kv_heads, page_size, dv)
+    normalise = q_weight is not None
+    if normalise:
+        assert q_weight.numel() == dk and k_weight.numel() == dk and q_weight.dtype == k_weight.dtype
+    if rot:
+        _i32(positions, "positions")
+        assert freq.dtype == torch.float32 and freq.is_contiguous() and tuple(freq.shape) == (rot // 2, 2)
+    q_out = torch.empty((T, q_units * dk), dtype=dtype, device=q.device)
+    lib = variants()
+    _check(lib, lib.coheryn_unit_norm_rope_kv_write(
+        _ptr(q), _ptr(k), _ptr(v), c_long(q.stride(0)), _ptr(q_weight), _ptr(k_weight),
+        c_int(_code(q_weight) if normalise else F32), c_float(eps), c_int(1 if normalise else 0), _ptr(positions), _ptr(freq),
+        c_int(rot), c_float(rot_scale), _ptr(q_out), c_int(_CODES[dtype]), c_long(q_out.stride(0)), _ptr(slots),
+        _ptr(k_cache), _ptr(v_cache), c_int(T), c_int(q_units), c_int(k_units), c_int(num_kv_heads), c_int(dk), c_int(dv),
+        c_int(page_size), _stream()))
+    return q_out
+
+
+def attention_maps(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
+                   num_heads: int, num_kv_heads: int, dk: int, dv: int, maps: int, page_size: int, window: Optional[int],
+                   chunk: Optional[int], sink: bool, scale: float, lam: float, head_norm: bool, eps: float,
+                   out_scale: float) -> None:
+    """Attention of every token of the step over its request's cache pages of ``group`` with ``maps`` score maps per
+    head (output a_0 - lam * a_1 for two), a mask by chunks (``chunk``: position i sees j <= i with i // chunk ==
+    j // chunk), by a window or causal, an optional sink term in the softmax's denominator, the head's output divided
+    by its root mean square over dv (``head_norm``) and multiplied by ``out_scale``.  q [T, heads * maps * dk],
+    out [T, heads * dv]; float32 arithmetic on either storage type."""
+    block_tables = step.block_tables[group]
+    _dev(q, out, k_cache, v_cache, block_tables, step.token_req, step.positions)
+    _i32(block_tables, "block_tables")
+    T = q.shape[0]
+    assert q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == num_heads * maps * dk and out.shape == (T, num_heads * dv)
+    assert k_cache.dtype == q.dtype and out.dtype == q.dtype and v_cache.dtype == q.dtype
+    lib = variants()
+    _check(lib, lib.coheryn_attention_maps(
+        _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache), c_int(_code(q)),
+        _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(step.token_req), _ptr(step.positions), c_int(T),
+        c_int(num_heads), c_int(num_kv_heads), c_int(dk), c_int(dv), c_int(maps), c_int(page_size), c_int(window or 0),
+        c_int(chunk or 0), c_int(1 if sink else 0), c_float(scale), c_float(lam), c_int(1 if head_norm else 0), c_float(eps),
+        c_float(out_scale), _stream()))

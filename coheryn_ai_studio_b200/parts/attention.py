@@ -219,5 +219,123 @@ class DistanceBiasAttention(Mixer):
         return out if self.partial_output else out[0]
 
 
+class MapsAttention(Mixer):
+    """Grouped-query causal attention with ``maps`` score maps per head (1: ordinary; 2: differential attention).
+
+    A query head carries ``maps`` queries of ``head_dim`` channels and a key/value head ``maps`` keys, laid out head by
+    head as [map 0, map 1]; all maps of a head attend over the SAME values.  With a_0, a_1 the maps' outputs the head
+    gives a_0 - lambda a_1, lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + ``lambda_init`` (one number for the layer, from
+    four vectors of ``head_dim`` entries), divided by its root mean square over the value channels (no weight) and
+    multiplied by 1 - ``lambda_init``.  Options, all independent of the number of maps:
+
+    * ``qk_norm = "head"``: every query and key map is divided by its root mean square over ``head_dim`` and multiplied
+      by a weight (``q.norm``, ``k.norm``: [head_dim], shared by the heads);
+    * ``position``: a rotation of the first ``rotary_dim`` channels of every map of q and k (none: positions do not
+      enter the scores);
+    * mask: ``chunk`` (i sees j <= i with i // chunk == j // chunk, counted from position 0 of the sequence), else
+      ``window`` (i - j < window), else every j <= i;
+    * ``sink``: the softmax's denominator has one more term exp(0), which carries no value;
+    * ``head_norm``: the division by the root mean square for a single map too; ``out_factor`` multiplies the output.
+
+    A layer may read the keys (as the cache holds them, rotated) and values that an earlier one wrote; it then has no
+    key and value projections.  The output product is float32 when ``float32_output`` (a block that normalises it)."""
+
+    output_parts = 1
+
+    def __init__(self, runtime: Runtime, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 v_head_dim: Optional[int], scale: float, maps: int = 1, lambda_init: Optional[float] = None,
+                 chunk: Optional[int] = None, window: Optional[int] = None, sink: bool = False, qk_norm: Optional[str] = None,
+                 head_norm: Optional[bool] = None, out_factor: float = 1.0, eps: float = 1e-6, own_kv: bool = True,
+                 float32_output: bool = False, out_scale: float = 1.0, position: Optional[Position] = None):
+        super().__init__(runtime)
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} heads do not divide into {num_kv_heads} kv heads")
+        if maps not in (1, 2):
+            raise ValueError("an attention head has one score map or two")
+        if maps == 2 and lambda_init is None:
+            raise ValueError("two score maps need the constant of their difference (lambda_init)")
+        if qk_norm not in (None, "head"):
+            raise ValueError(f"qk_norm {qk_norm!r} is not built here (None, 'head')")
+        for name, v in (("chunk", chunk), ("window", window)):
+            if v is not None and v < 1:
+                raise ValueError(f"an attention {name} must hold at least one position")
+        self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
+        self.dk, self.dv = int(head_dim), int(v_head_dim if v_head_dim is not None else head_dim)
+        self.maps, self.scale, self.eps = int(maps), float(scale), float(eps)
+        self.lambda_init = float(lambda_init) if lambda_init is not None else 0.0
+        self.chunk, self.window, self.sink, self.qk_norm = chunk, window, bool(sink), qk_norm
+        self.head_norm = bool(head_norm) if head_norm is not None else self.maps == 2
+        self.out_factor = float(out_factor) * float(out_scale) * ((1.0 - self.lambda_init) if self.maps == 2 else 1.0)
+        self.own_kv, self.position = bool(own_kv), position
+        if position is not None and position.rotary_dim > self.dk:
+            raise ValueError(f"{position.rotary_dim} rotated channels do not fit a map of {self.dk}")
+        self.out_dtype = torch.float32 if float32_output else None
+        self.lam = 0.0
+        self.w_qkv = self.w_o = self.q_norm = self.k_norm = None
+
+    def cache_requirement(self):
+        # a page keeps every position: a chunk's keys are needed until the chunk ends, a window's while it passes
+        return PagedKV(self.num_kv_heads, self.maps * self.dk, self.window if self.chunk is None else None, self.dv)
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        W, H, G, dk, dv, M = self.hidden_size, self.num_heads, self.num_kv_heads, self.dk, self.dv, self.maps
+        specs = {"q": TensorSpec((H * M * dk, W)), "o": TensorSpec((W, H * dv))}
+        if self.own_kv:
+            specs["k"] = TensorSpec((G * M * dk, W))
+            specs["v"] = TensorSpec((G * dv, W))
+        if self.qk_norm is not None:
+            specs["q.norm"] = TensorSpec((dk,), role="vector", init="norm")
+            specs["k.norm"] = TensorSpec((dk,), role="vector", init="norm")
+        if M == 2:
+            for name in ("lq1", "lk1", "lq2", "lk2"):
+                specs[name] = TensorSpec((dk,), role="vector", init="bias")
+        return specs
+
+    def bind(self, tensors):
+        mats = [tensors["q"]] + ([tensors["k"], tensors["v"]] if self.own_kv else [])
+        self.w_qkv = torch.cat(mats, dim=0).contiguous() if len(mats) > 1 else mats[0]
+        self.w_o = tensors["o"]
+        if self.qk_norm is not None:
+            qn, kn = tensors["q.norm"], tensors["k.norm"]
+            dt = torch.float32 if torch.float32 in (qn.dtype, kn.dtype) else qn.dtype
+            self.q_norm, self.k_norm = qn.to(dt).contiguous(), kn.to(dt).contiguous()
+        if self.maps == 2:
+            import math
+            d = lambda a, b: float((tensors[a].double() * tensors[b].double()).sum().item())
+            self.lam = math.exp(d("lq1", "lk1")) - math.exp(d("lq2", "lk2")) + self.lambda_init
+
+    def output_weights(self):
+        return [self.w_o]
+
+    def forward_open(self, x: torch.Tensor, step: StepContext, cache: LayerCache, outs) -> None:
+        """The heads' outputs in front of the output product into ``outs[0]`` ([T, heads * dv], rows may be strided)."""
+        Attention._check(cache)
+        if cache.writes != self.own_kv:
+            raise ValueError("an attention with key and value projections writes its cache; one without reads another's")
+        H, G, dk, dv, M = self.num_heads, self.num_kv_heads, self.dk, self.dv, self.maps
+        nq, nk = H * M * dk, G * M * dk
+        proj = ops.linear(x, self.w_qkv, out_dtype=torch.float32)
+        pos = self.position
+        rot = pos.rotary_dim if pos is not None else 0
+        q = ops.unit_norm_rope_kv_write(
+            proj[:, :nq], proj[:, nq:nq + nk] if self.own_kv else None, proj[:, nq + nk:] if self.own_kv else None,
+            self.q_norm, self.k_norm, self.eps, step.positions, pos.frequency_pairs() if pos is not None else None, rot,
+            pos.amplitude if pos is not None else 1.0, step.slots[cache.group] if self.own_kv else None, cache.k, cache.v,
+            H * M, G * M, G, dk, dv, cache.page_size, self.runtime.dtype)
+        ops.attention_maps(q, outs[0], cache.k, cache.v, step, cache.group, H, G, dk, dv, M, cache.page_size, self.window,
+                           self.chunk, self.sink, self.scale, self.lam, self.head_norm, self.eps, self.out_factor)
+
+    def forward_into(self, x: torch.Tensor, step: StepContext, cache: LayerCache, out: torch.Tensor) -> None:
+        o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
+        self.forward_open(x, step, cache, [o])
+        ops.linear(o, self.w_o, out=out[0])
+
+    def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+        o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
+        self.forward_open(x, step, cache, [o])
+        return ops.linear(o, self.w_o, out_dtype=self.out_dtype, partial_ok=self.partial_output)
+
+
+register_mixer("attention_maps", MapsAttention)
 register_mixer("attention", Attention)
 register_mixer("attention_distance_bias", DistanceBiasAttention)

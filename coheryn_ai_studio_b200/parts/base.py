@@ -112,6 +112,41 @@ class StepContext:
     native: Optional[object] = None
 
 
+@dataclass
+class NormedSum:
+    """A producer's output that is a sum of normalised summands, not yet formed:
+    y = coef * sum_p parts[p] / rms(parts[p]) * weights[p], rms over the last axis with ``eps`` inside the root.
+    ``parts`` float32 [P, T, H], ``weights`` [P, H]."""
+
+    parts: torch.Tensor
+    weights: torch.Tensor
+    coef: float
+    eps: float
+
+    def resolve(self) -> torch.Tensor:
+        """The sum itself, by library operations (traces and tests; the product path hands the object on)."""
+        p = self.parts.float()
+        y = p * torch.rsqrt((p * p).mean(-1, keepdim=True) + self.eps) * self.weights.float().unsqueeze(1)
+        return y.sum(0) * self.coef
+
+
+@dataclass
+class PostNormed:
+    """A pending delta that is normalised before it is added: x += value / rms(value) * weight, where ``value`` is a
+    float32 tensor [T, H], a float32 stack [P, T, H] of partial sums, or a :class:`NormedSum`.  The norm that adds it
+    (``Norm.forward``) does both in one pass."""
+
+    value: object
+    weight: torch.Tensor
+    eps: float
+
+    def resolve(self) -> torch.Tensor:
+        v = self.value.resolve() if isinstance(self.value, NormedSum) else self.value.float()
+        if v.dim() == 3:
+            v = v.sum(0)
+        return v * torch.rsqrt((v * v).mean(-1, keepdim=True) + self.eps) * self.weight.float()
+
+
 # ------------------------------------------------------------------------------- parts
 class Part:
     # False if ``forward`` waits for the device (reads a result on the host) or launches work whose

@@ -12,7 +12,7 @@ from typing import Dict
 import torch
 
 from .. import ops
-from .base import Arrangement, Part, register_arrangement
+from .base import Arrangement, Part, PostNormed, register_arrangement
 from .native_block import NativeBlock
 
 
@@ -121,5 +121,41 @@ class ParallelResidual(Arrangement):
         return residual, out
 
 
+class SandwichResidual(Arrangement):
+    """A norm before and after each sub-layer: x += mixer_post_norm(mixer(mixer_norm(x))), then
+    x += feed_forward_post_norm(feed_forward(feed_forward_norm(x))); the feed-forward with its two norms may be absent.
+    A sub-layer's output is handed on as a pending :class:`PostNormed` delta, and the NEXT norm (this block's, the
+    following block's or the model's last) normalises it, adds it to the float32 stream and normalises the sum in one
+    kernel, so the block costs one norm kernel per sub-layer like the pre-norm block."""
+
+    SLOTS = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm", "feed_forward_norm": "norm",
+             "feed_forward": "feed_forward", "feed_forward_post_norm": "norm"}
+    OPTIONAL = ("feed_forward_norm", "feed_forward", "feed_forward_post_norm")
+    NAMES = {"mixer_norm": "pre_mixer_norm", "mixer": "mixer", "mixer_post_norm": "post_mixer_norm",
+             "feed_forward_norm": "pre_feed_forward_norm", "feed_forward": "feed_forward",
+             "feed_forward_post_norm": "post_feed_forward_norm"}
+
+    def __init__(self, parts):
+        super().__init__(parts)
+        ff = [self.slots.get(n) is not None for n in ("feed_forward_norm", "feed_forward", "feed_forward_post_norm")]
+        if any(ff) and not all(ff):
+            raise ValueError("sandwich_residual: a feed-forward comes with both of its norms or not at all")
+
+    def parts(self) -> Dict[str, Part]:
+        names = self.names or self.NAMES
+        return {names[slot]: part for slot, part in self.slots.items()}
+
+    def forward(self, residual, delta, step, cache):
+        h = self.mixer_norm.forward(residual, delta)
+        post = self.mixer_post_norm
+        delta = PostNormed(self.mixer.forward(h, step, cache), post.weight, post.eps)
+        if self.feed_forward is not None:
+            h = self.feed_forward_norm.forward(residual, delta)
+            post = self.feed_forward_post_norm
+            delta = PostNormed(self.feed_forward.forward(h, step), post.weight, post.eps)
+        return residual, delta
+
+
+register_arrangement("sandwich_residual", SandwichResidual)
 register_arrangement("prenorm_residual", PreNormResidual)
 register_arrangement("parallel_residual", ParallelResidual)

@@ -1,6 +1,7 @@
 """Dense gated feed-forward: y = W_down (act(W_gate x) * (W_up x)), no biases; act = silu (SwiGLU),
 silu(g) = g / (1 + exp(-g)), or the tanh form of GELU, in float32
-(crates/coheryn-engine/src/inference.rs:516-540, crates/coheryn-engine/src/cpu.rs:74-78).
+(crates/coheryn-engine/src/inference.rs:516-540, crates/coheryn-engine/src/cpu.rs:74-78).  ``swish_clamped`` with its
+constant c is the variant g <- min(g, c), u <- clamp(u, -c, c), y = W_down (g sigmoid(1.702 g) (u + 1)).
 """
 from __future__ import annotations
 
@@ -15,12 +16,16 @@ from .base import FeedForward, Runtime, StepContext, register_feed_forward
 
 class GatedMLP(FeedForward):
     def __init__(self, runtime: Runtime, hidden_size: int, intermediate_size: int, activation: str,
-                 tensors=("gate_proj.weight", "up_proj.weight", "down_proj.weight")):
-        """``tensors``: the local names of the gate, up and down matrices in the checkpoint."""
+                 tensors=("gate_proj.weight", "up_proj.weight", "down_proj.weight"), activation_constant=None,
+                 float32_output: bool = False):
+        """``tensors``: the local names of the gate, up and down matrices in the checkpoint.  ``activation_constant``:
+        the constant of an activation that has one.  ``float32_output``: the down projection hands its result on in
+        float32 (a block that normalises it before the residual add wants that)."""
         super().__init__(runtime)
         self.names = tuple(tensors)
-        ops.gated_activation_code(activation)     # refuses, by name, an activation the epilogues lack
-        self.activation = activation
+        ops.gated_epilogue_word(activation, activation_constant)     # refuses an activation the epilogues lack
+        self.activation, self.constant = activation, activation_constant
+        self.out_dtype = torch.float32 if float32_output else None
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
         self.w_gate_up = self.w_down = None
 
@@ -37,8 +42,8 @@ class GatedMLP(FeedForward):
         self.w_down = tensors[self.names[2]]
 
     def forward(self, x: torch.Tensor, step: StepContext) -> torch.Tensor:
-        act = ops.gated_linear(x, self.w_gate_up, self.activation)
-        return ops.linear(act, self.w_down, partial_ok=self.partial_output)
+        act = ops.gated_linear(x, self.w_gate_up, self.activation, param=self.constant)
+        return ops.linear(act, self.w_down, out_dtype=self.out_dtype, partial_ok=self.partial_output)
 
     output_parts = 1
 
@@ -48,11 +53,11 @@ class GatedMLP(FeedForward):
         return [self.w_down]
 
     def forward_open(self, x: torch.Tensor, step: StepContext, cache, outs) -> None:
-        ops.gated_linear(x, self.w_gate_up, self.activation, out=outs[0])
+        ops.gated_linear(x, self.w_gate_up, self.activation, out=outs[0], param=self.constant)
 
     def forward_into(self, x: torch.Tensor, step: StepContext, out: torch.Tensor) -> None:
         """The output written into ``out`` (float32 [1, T, H]): one of the summands that a block hands to the next norm."""
-        ops.linear(ops.gated_linear(x, self.w_gate_up, self.activation), self.w_down, out=out[0])
+        ops.linear(ops.gated_linear(x, self.w_gate_up, self.activation, param=self.constant), self.w_down, out=out[0])
 
 
 register_feed_forward("gated_mlp", GatedMLP)

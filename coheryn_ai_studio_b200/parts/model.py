@@ -141,7 +141,12 @@ class DecoderModel:
             else:
                 residual, delta = layer.forward(residual, delta, step, cache)
             if self.layer_observer is not None:
-                out = residual if delta is None else residual + (delta.sum(0) if delta.dim() == 3 else delta.float())
+                if delta is None:
+                    out = residual
+                elif hasattr(delta, "resolve"):      # a summand that is normalised before it is added
+                    out = residual + delta.resolve()
+                else:
+                    out = residual + (delta.sum(0) if delta.dim() == 3 else delta.float())
                 self.layer_observer(i, out)
         R = logit_rows.numel()
         if R == 0:

@@ -166,7 +166,9 @@ class NativeBlock:
         if n1.size != H or n2.size != H or f.hidden_size != H or n1.weight.shape != (H,) or n2.weight.shape != (H,):
             return None
         try:
-            gated = ops.gated_activation_code(f.activation)
+            if f.out_dtype is not None:
+                return None
+            gated = ops.gated_epilogue_word(f.activation, f.constant)
             lib = ops.attention_lib(m.head_dim)
         except Exception:
             return None

@@ -12,7 +12,7 @@ import torch
 
 from .. import ops
 from ..weights.spec import TensorSpec
-from .base import Norm, Runtime, register_norm
+from .base import Norm, NormedSum, PostNormed, Runtime, register_norm
 
 
 class RMSNorm(Norm):
@@ -35,8 +35,27 @@ class RMSNorm(Norm):
         the compute dtype.  With ``rows`` only those rows are produced."""
         n = residual.shape[0] if rows is None else rows.numel()
         out = torch.empty((n, self.size), dtype=self.runtime.dtype, device=residual.device)
+        if isinstance(delta, PostNormed):     # a summand that is normalised before it is added: one kernel for both norms
+            apply_post_normed(residual, delta, self.weight, self.eps, out, rows)
+            return out
         ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows=rows)
         return out
+
+
+def apply_post_normed(residual, delta: PostNormed, weight, eps: float, out, rows=None) -> None:
+    """residual += delta.value / rms(delta.value) * delta.weight (without ``rows``); ``out`` = the normalised sum times
+    ``weight`` (both may be None: the residual is only updated).  The two norms share one ``eps``."""
+    if weight is not None and float(eps) != float(delta.eps):
+        raise ValueError("a summand's norm and the norm that adds it are fused and must share their eps")
+    v = delta.value
+    if isinstance(v, NormedSum):
+        if float(v.eps) != float(delta.eps):
+            raise ValueError("the norms of a sum of normalised summands and the norm over it must share their eps")
+        ops.add_normed_rmsnorm(residual, v.parts, v.weights, v.coef, delta.weight, weight, delta.eps, out, rows=rows)
+    else:
+        if v.dtype != torch.float32:
+            v = v.float()
+        ops.add_normed_rmsnorm(residual, v, None, 1.0, delta.weight, weight, delta.eps, out, rows=rows)
 
 
 register_norm("rmsnorm", RMSNorm)

@@ -45,4 +45,63 @@ class RotateHalfRope(Position):
         return self._table
 
 
+class ComputedRope(Position):
+    """Rotate-half rotary encoding whose angles the kernels compute from the position (no table, so no bound on
+    positions): pair i of the first ``rotary_dim`` channels turns by position * f_i, f_i = theta^(-2i / rotary_dim).
+
+    ``scaling`` (optional) is the YaRN interpolation by parts: with d(t) = rotary_dim * ln(original / (2 pi t)) /
+    (2 ln theta), lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)), rotary_dim - 1) and
+    ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency becomes f_i / factor * ramp_i + f_i (1 - ramp_i)
+    and cos and sin are multiplied by 0.1 ln(factor) + 1.
+
+    The frequencies are made in float64 and handed to the device as a float32 pair (high, low) each; the kernel
+    forms position * (high + low) without losing the low part, so the angle is good to float32's last bit at any
+    position."""
+
+    def __init__(self, runtime: Runtime, rotary_dim: int, theta: float, scaling=None):
+        super().__init__(runtime)
+        if rotary_dim % 2 or rotary_dim < 2:
+            raise ValueError(f"rotary_dim {rotary_dim} must be even and positive")
+        if not theta > 1:
+            raise ValueError("the base of the frequencies must exceed 1")
+        self.rotary_dim, self.theta = int(rotary_dim), float(theta)
+        self.scaling = dict(scaling) if scaling else None
+        if self.scaling is not None:
+            for key in ("factor", "original", "fast", "slow"):
+                if not float(self.scaling.get(key, 0)) > 0:
+                    raise ValueError(f"rotary scaling needs a positive {key!r}")
+        self._freq = None
+
+    def frequencies(self) -> np.ndarray:
+        """float64 [rotary_dim / 2]."""
+        import math
+        dims, half = self.rotary_dim, self.rotary_dim // 2
+        i = np.arange(half, dtype=np.float64)
+        f = np.power(np.float64(self.theta), -2.0 * i / dims)
+        if self.scaling is not None:
+            s = self.scaling
+            where = lambda t: dims * math.log(float(s["original"]) / (2.0 * math.pi * float(t))) / (2.0 * math.log(self.theta))
+            lo = max(math.floor(where(s["fast"])), 0)
+            hi = min(math.ceil(where(s["slow"])), dims - 1)
+            ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+            f = f / float(s["factor"]) * ramp + f * (1.0 - ramp)
+        return f
+
+    @property
+    def amplitude(self) -> float:
+        """What cos and sin are multiplied by."""
+        import math
+        return 0.1 * math.log(float(self.scaling["factor"])) + 1.0 if self.scaling is not None else 1.0
+
+    def frequency_pairs(self) -> torch.Tensor:
+        """float32 [rotary_dim / 2, 2] on the device: each frequency as high + low."""
+        if self._freq is None:
+            f = self.frequencies()
+            high = f.astype(np.float32)
+            low = (f - high.astype(np.float64)).astype(np.float32)
+            self._freq = torch.from_numpy(np.ascontiguousarray(np.stack([high, low], axis=-1))).to(self.runtime.device)
+        return self._freq
+
+
 register_position("rope_rotate_half", RotateHalfRope)
+register_position("rope_computed", ComputedRope)

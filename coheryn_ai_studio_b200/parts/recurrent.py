@@ -30,7 +30,7 @@ import torch
 from .. import ops
 from ..config.spec import PartSpec
 from ..weights.spec import TensorSpec
-from .base import MIXERS, FixedState, LayerCache, Mixer, Runtime, StepContext, build_part, register_mixer
+from .base import MIXERS, FixedState, LayerCache, Mixer, NormedSum, Runtime, StepContext, build_part, register_mixer
 
 
 class _StackedInput:
@@ -117,9 +117,13 @@ class MatrixMemory(_StateMixer):
 class GatedDeltaRule(_StateMixer):
     def __init__(self, runtime: Runtime, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  v_head_dim: int, conv_taps: int, eps: float, decay_rank: Optional[int] = None,
-                 gate_rank: Optional[int] = None, out_scale: float = 1.0):
+                 gate_rank: Optional[int] = None, out_scale: float = 1.0, decay: str = "channel", low_rank: bool = True,
+                 gate_activation: str = "sigmoid"):
         """``decay_rank`` / ``gate_rank``: the inner sizes of the two-step projections of the decay and of the output
-        gate; None takes them from the checkpoint's tensors."""
+        gate; None takes them from the checkpoint's tensors.  ``decay``: "channel" (a decay per head and key channel) or
+        "head" (one per head: ``dt_bias`` then has one entry per head).  ``low_rank`` False: the decay's and the gate's
+        pre-activations are single projections ``a`` and ``g`` of the input instead of two-step ones.
+        ``gate_activation``: what the output gate's pre-activation passes, "sigmoid" or "silu"."""
         super().__init__(runtime)
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads do not divide into {num_kv_heads} query/key heads")
@@ -128,6 +132,10 @@ class GatedDeltaRule(_StateMixer):
         self.hidden_size, self.num_heads, self.num_kv_heads = int(hidden_size), int(num_heads), int(num_kv_heads)
         self.dk, self.dv, self.taps, self.eps, self.out_scale = int(head_dim), int(v_head_dim), int(conv_taps), float(eps), float(out_scale)
         self.decay_rank, self.gate_rank = decay_rank, gate_rank
+        if decay not in ("channel", "head") or gate_activation not in ("sigmoid", "silu"):
+            raise ValueError("gated_delta_rule: decay is 'channel' or 'head', gate_activation 'sigmoid' or 'silu'")
+        self.decay, self.low_rank, self.gate_activation = decay, bool(low_rank), gate_activation
+        self.decay_size = self.num_heads * (self.dk if decay == "channel" else 1)
         self.channels = 2 * self.num_kv_heads * self.dk + self.num_heads * self.dv
         self.memory = self.num_heads * self.dk * self.dv
 
@@ -137,30 +145,39 @@ class GatedDeltaRule(_StateMixer):
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         W, H, G, dk, dv, n = self.hidden_size, self.num_heads, self.num_kv_heads, self.dk, self.dv, self.taps
         ra, rg = self.decay_rank or -1, self.gate_rank or -1      # -1: any size, as the checkpoint has it
-        return {"q": TensorSpec((G * dk, W)), "q.conv": TensorSpec((G * dk, n), role="vector", init="conv"),
-                "k": TensorSpec((G * dk, W)), "k.conv": TensorSpec((G * dk, n), role="vector", init="conv"),
-                "v": TensorSpec((H * dv, W)), "v.conv": TensorSpec((H * dv, n), role="vector", init="conv"),
-                "b": TensorSpec((H, W)), "A_log": TensorSpec((H,), role="vector", init="bias"),
-                "norm": TensorSpec((dv,), role="vector", init="norm"),
-                "a1": TensorSpec((ra, W)), "a2": TensorSpec((H * dk, ra)),
-                "dt_bias": TensorSpec((H * dk,), role="vector", init="bias"),
-                "g1": TensorSpec((rg, W)), "g2": TensorSpec((H * dv, rg)), "o": TensorSpec((W, H * dv))}
+        specs = {"q": TensorSpec((G * dk, W)), "q.conv": TensorSpec((G * dk, n), role="vector", init="conv"),
+                 "k": TensorSpec((G * dk, W)), "k.conv": TensorSpec((G * dk, n), role="vector", init="conv"),
+                 "v": TensorSpec((H * dv, W)), "v.conv": TensorSpec((H * dv, n), role="vector", init="conv"),
+                 "b": TensorSpec((H, W)), "A_log": TensorSpec((H,), role="vector", init="bias"),
+                 "norm": TensorSpec((dv,), role="vector", init="norm"),
+                 "dt_bias": TensorSpec((self.decay_size,), role="vector", init="bias"), "o": TensorSpec((W, H * dv))}
+        if self.low_rank:
+            specs.update({"a1": TensorSpec((ra, W)), "a2": TensorSpec((self.decay_size, ra)),
+                          "g1": TensorSpec((rg, W)), "g2": TensorSpec((H * dv, rg))})
+        else:
+            specs.update({"a": TensorSpec((self.decay_size, W)), "g": TensorSpec((H * dv, W))})
+        return specs
 
     def bind(self, tensors):
-        if tensors["a1"].shape[0] != tensors["a2"].shape[1] or tensors["g1"].shape[0] != tensors["g2"].shape[1]:
-            raise ValueError("the two steps of a low-rank projection do not fit each other")
-        self.stacked = _StackedInput([(n, tensors[n]) for n in ("q", "k", "v", "b", "a1", "g1")])
         convs = [tensors["q.conv"], tensors["k.conv"], tensors["v.conv"]]
         dt = torch.float32 if any(c.dtype == torch.float32 for c in convs) else convs[0].dtype
         self.conv_w = torch.cat([c.to(dt) for c in convs], dim=0).contiguous()
+        self.w_o = tensors["o"]
+        self.rate_log, self.dt_bias, self.norm_w = tensors["A_log"], tensors["dt_bias"], tensors["norm"]
+        if not self.low_rank:
+            self.stacked = _StackedInput([(n, tensors[n]) for n in ("q", "k", "v", "b", "a", "g")])
+            self.w_second = None
+            return
+        if tensors["a1"].shape[0] != tensors["a2"].shape[1] or tensors["g1"].shape[0] != tensors["g2"].shape[1]:
+            raise ValueError("the two steps of a low-rank projection do not fit each other")
+        self.stacked = _StackedInput([(n, tensors[n]) for n in ("q", "k", "v", "b", "a1", "g1")])
         # The second steps of the two low-rank projections as ONE product: [a1 h | g1 h] (neighbours in the stacked
         # output) times the block-diagonal matrix of a2 and g2 (exact zeros elsewhere) gives [step | gate].
         a2, g2 = tensors["a2"], tensors["g2"]
         both = torch.zeros((a2.shape[0] + g2.shape[0], a2.shape[1] + g2.shape[1]), dtype=a2.dtype, device=a2.device)
         both[:a2.shape[0], :a2.shape[1]] = a2
         both[a2.shape[0]:, a2.shape[1]:] = g2
-        self.w_second, self.w_o = both.contiguous(), tensors["o"]
-        self.rate_log, self.dt_bias, self.norm_w = tensors["A_log"], tensors["dt_bias"], tensors["norm"]
+        self.w_second = both.contiguous()
 
     def output_weights(self):
         return [self.w_o]
@@ -175,21 +192,35 @@ class GatedDeltaRule(_StateMixer):
         st, proj = self.stacked, self.stacked.project(x)
         G, H, dk, dv = self.num_kv_heads, self.num_heads, self.dk, self.dv
         qkv = ops.short_conv_silu(st.cut(proj, "q", "v"), self.conv_w, state[:, self.memory:], step)
-        second = ops.linear(st.cut(proj, "a1", "g1"), self.w_second, out_dtype=torch.float32)
-        step_pre, gate = second[:, :H * dk], second[:, H * dk:]
+        if self.low_rank:
+            second = ops.linear(st.cut(proj, "a1", "g1"), self.w_second, out_dtype=torch.float32)
+            step_pre, gate = second[:, :self.decay_size], second[:, self.decay_size:]
+        else:
+            step_pre, gate = st.cut(proj, "a"), st.cut(proj, "g")
         o = outs[0]
         ops.gated_delta_scan(qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], st.cut(proj, "b"), step_pre,
                              self.dt_bias, self.rate_log, state[:, :self.memory], step, H, G, dk, dv, o, self.norm_w, gate,
-                             self.eps, self.out_scale)
+                             self.eps, self.out_scale, decay_per_channel=self.decay == "channel",
+                             gate_activation=self.gate_activation)
 
 
 class SideBySide(Mixer):
-    def __init__(self, runtime: Runtime, hidden_size: int, mixers: Sequence[Tuple[str, PartSpec, float]], position=None):
-        """``mixers``: (name under which the child's tensors stand, the child's PartSpec, the weight of its output)."""
+    def __init__(self, runtime: Runtime, hidden_size: int, mixers: Sequence[Tuple[str, PartSpec, float]], position=None,
+                 combine: str = "sum", eps: float = 1e-6):
+        """``mixers``: (name under which the child's tensors stand, the child's PartSpec, the weight of its output).
+        ``combine``: "sum" (the weighted sum of the children's outputs) or "normed_mean": every child's output is
+        divided by its root mean square over the model width (``eps`` inside the root) and multiplied by a weight
+        ``<name>.out`` [width]; the result is the mean of those (the children's weights must be 1)."""
         super().__init__(runtime)
         self.hidden_size = int(hidden_size)
         if not mixers:
             raise ValueError("side_by_side needs at least one mixer")
+        if combine not in ("sum", "normed_mean"):
+            raise ValueError(f"side_by_side: combine {combine!r} is not built (sum, normed_mean)")
+        if combine == "normed_mean" and any(float(w) != 1.0 for _, _, w in mixers):
+            raise ValueError("side_by_side: normalised outputs take no weights besides their norms'")
+        self.combine, self.eps = combine, float(eps)
+        self.out_weights = None
         self.children = []
         for name, spec, weight in mixers:
             extra = {"position": position} if position is not None else {}
@@ -204,13 +235,26 @@ class SideBySide(Mixer):
         return tuple(c.cache_requirement() for _, c in self.children)
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {f"{name}.{local}": ts for name, c in self.children for local, ts in c.tensor_specs().items()}
+        specs = {f"{name}.{local}": ts for name, c in self.children for local, ts in c.tensor_specs().items()}
+        if self.combine == "normed_mean":
+            for name, _ in self.children:
+                specs[f"{name}.out"] = TensorSpec((self.hidden_size,), role="vector", init="norm")
+        return specs
 
     def bind(self, tensors):
         for name, c in self.children:
             c.bind({local: tensors[f"{name}.{local}"] for local in c.tensor_specs() if f"{name}.{local}" in tensors})
+        if self.combine == "normed_mean":
+            ws = [tensors[f"{name}.out"] for name, _ in self.children]
+            dt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
+            self.out_weights = torch.stack([w.to(dt) for w in ws], dim=0).contiguous()
 
     def forward_into(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], out: torch.Tensor) -> None:
+        if self.combine != "sum":
+            raise ValueError("side_by_side: normalised outputs are not summands of a block's sum; use forward")
+        self._children_into(x, step, cache, out)
+
+    def _children_into(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], out: torch.Tensor) -> None:
         if cache is None or cache.kind != "several" or len(cache.parts) != len(self.children):
             raise ValueError("side_by_side needs one cache per child")
         at = 0
@@ -219,8 +263,8 @@ class SideBySide(Mixer):
             at += c.output_parts
 
     def output_weights(self):
-        if not all(hasattr(c, "output_weights") for _, c in self.children):
-            return None
+        if self.combine != "sum" or not all(hasattr(c, "output_weights") for _, c in self.children):
+            return None      # normalised outputs cannot be joined into one product
         return [w for _, c in self.children for w in c.output_weights()]
 
     def forward_open(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache], outs) -> None:
@@ -234,7 +278,11 @@ class SideBySide(Mixer):
 
     def forward(self, x: torch.Tensor, step: StepContext, cache: Optional[LayerCache]) -> torch.Tensor:
         out = torch.empty((self.output_parts, x.shape[0], self.hidden_size), dtype=torch.float32, device=x.device)
-        self.forward_into(x, step, cache, out)
+        self._children_into(x, step, cache, out)
+        if self.combine == "normed_mean":
+            if self.output_parts != len(self.children):
+                raise ValueError("side_by_side: a child with several summands cannot be normalised as one")
+            return NormedSum(out, self.out_weights, 1.0 / len(self.children), self.eps)
         if self.partial_output:
             return out
         raise ValueError("side_by_side hands its children's outputs on as summands and needs norms that add them")
