@@ -50,10 +50,11 @@ unit_norm_rope_kv_write_kernel(const float* __restrict__ q, const float* __restr
       const float fh = freq[2 * i], fl = freq[2 * i + 1];
       const float ah = p * fh;
       const float al = fmaf(p, fh, -ah) + p * fl;      // what the rounding of p * fh lost, and the low part
-      float s, c;
+      float s, c, sl, cl;
       sincosf(ah, &s, &c);
-      cs[2 * i] = (c - s * al) * rot_scale;
-      cs[2 * i + 1] = (s + c * al) * rot_scale;
+      sincosf(al, &sl, &cl);                           // |al| is at most half a unit in the last place of ah
+      cs[2 * i] = (c * cl - s * sl) * rot_scale;
+      cs[2 * i + 1] = (s * cl + c * sl) * rot_scale;
     }
   }
   const float* qr = q + t * ld;

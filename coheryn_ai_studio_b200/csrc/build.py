@@ -248,10 +248,23 @@ def variants_library() -> ctypes.CDLL:
     return load_library("variants", VARIANT_SOURCES)
 
 
+def maps_attention_library(dk: int, dv: int, maps: int) -> ctypes.CDLL:
+    """The tensor-core kernels of the attention with score maps, compiled for one (channels per map, value channels,
+    maps) when a model needs them."""
+    if dk % 16 or dv % 16 or not 16 <= dk <= 256 or not 16 <= dv <= 256 or maps not in (1, 2):
+        raise BuildError(f"the tensor-core attention with score maps takes head sizes 16..256 in steps of 16 and one or "
+                         f"two maps, not ({dk}, {dv}, {maps})")
+    return load_library(f"maps_{dk}_{dv}_{maps}", ["attention_maps_tc.cu", "runtime.cu"],
+                        {"CO_MAPS_DK": dk, "CO_MAPS_DV": dv, "CO_MAPS_N": maps})
+
+
 def build_all(head_dims: Sequence[int] = (16, 32, 64, 128)) -> List[str]:
     """Compile everything ahead of time (no GPU needed)."""
     paths = [build_host_library(), build_library("core", CORE_SOURCES), build_library("recurrent", RECURRENT_SOURCES),
              build_library("variants", VARIANT_SOURCES)]
+    for dk, dv, maps in ((64, 128, 2), (64, 64, 1)):
+        paths.append(build_library(f"maps_{dk}_{dv}_{maps}", ["attention_maps_tc.cu", "runtime.cu"],
+                                   {"CO_MAPS_DK": dk, "CO_MAPS_DV": dv, "CO_MAPS_N": maps}))
     for hd in head_dims:
         paths.append(build_library(f"attn_hd{hd}", ["attention_bf16.cu", "attention_tc.cu", "runtime.cu"],
                                    {"CO_HEAD_DIM": hd}))

@@ -55,7 +55,7 @@ def launch_count() -> int:
 def total_launch_count() -> int:
     """Kernel launches made through every library of this package that is loaded."""
     n = launch_count()
-    for lib in list(_attn_libs.values()) + [l for l in (_recurrent, _variants) if l is not None]:
+    for lib in list(_attn_libs.values()) + list(_maps_libs.values()) + [l for l in (_recurrent, _variants) if l is not None]:
         n += int(lib.coheryn_launch_count())
     return n
 
@@ -1150,10 +1150,37 @@ def unit_norm_rope_kv_write(q, k, v, q_weight, k_weight, eps: float, positions, 
     return q_out
 
 
+_maps_libs = {}
+# Whether bfloat16 steps take the tensor-core kernels of the attention with score maps (the float32-arithmetic kernel
+# otherwise); for tests and measurements.
+MAPS_TC = os.environ.get("COHERYN_MAPS_TC", "1") != "0"
+
+
+def set_maps_tc(on: bool) -> None:
+    global MAPS_TC
+    MAPS_TC = bool(on)
+
+
+def maps_attention_lib(dk: int, dv: int, maps: int):
+    key = (dk, dv, maps)
+    lib = _maps_libs.get(key)
+    if lib is None:
+        lib = build.maps_attention_library(dk, dv, maps)
+        lib.coheryn_last_error.restype = ctypes.c_char_p
+        lib.coheryn_launch_count.restype = ctypes.c_ulonglong
+        lib.coheryn_maps_scratch_floats.restype = ctypes.c_long
+        got = [ctypes.c_int(), ctypes.c_int(), ctypes.c_int()]
+        lib.coheryn_maps_shape(*[ctypes.byref(g) for g in got])
+        if tuple(g.value for g in got) != key:
+            raise KernelError(f"the attention library was built for {tuple(g.value for g in got)}, not {key}")
+        _maps_libs[key] = lib
+    return lib
+
+
 def attention_maps(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, step, group: int,
                    num_heads: int, num_kv_heads: int, dk: int, dv: int, maps: int, page_size: int, window: Optional[int],
                    chunk: Optional[int], sink: bool, scale: float, lam: float, head_norm: bool, eps: float,
-                   out_scale: float) -> None:
+                   out_scale: float, force_simple: bool = False) -> None:
     """Attention of every token of the step over its request's cache pages of ``group`` with ``maps`` score maps per
     head (output a_0 - lam * a_1 for two), a mask by chunks (``chunk``: position i sees j <= i with i // chunk ==
     j // chunk), by a window or causal, an optional sink term in the softmax's denominator, the head's output divided
@@ -1165,6 +1192,26 @@ def attention_maps(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
     T = q.shape[0]
     assert q.stride(1) == 1 and out.stride(1) == 1 and q.shape[1] == num_heads * maps * dk and out.shape == (T, num_heads * dv)
     assert k_cache.dtype == q.dtype and out.dtype == q.dtype and v_cache.dtype == q.dtype
+    q_lens = getattr(step, "q_lens", None)
+    fast = (MAPS_TC and not force_simple and q.dtype == torch.bfloat16 and dk % 16 == 0 and dv % 16 == 0 and 16 <= dk <= 256
+            and 16 <= dv <= 256 and q_lens and getattr(step, "max_kv_len", None) and getattr(step, "cu_q", None) is not None
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0)
+    if fast:
+        # rows that are whole runs of consecutive positions per request, ending at the request's last position
+        _i32(step.cu_q, "cu_q"); _i32(step.kv_lens, "kv_lens")
+        lib = maps_attention_lib(dk, dv, maps)
+        B = len(q_lens)
+        single = any(n == 1 for n in q_lens) and num_heads // num_kv_heads <= 16
+        floats = int(lib.coheryn_maps_scratch_floats(c_int(B), c_int(num_heads))) if single else 0
+        scratch = torch.empty(floats, dtype=torch.float32, device=q.device) if floats else None
+        _check(lib, lib.coheryn_attention_maps_bf16(
+            _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
+            c_int(block_tables.shape[1]), _ptr(step.cu_q), _ptr(step.kv_lens), c_int(B), c_int(num_heads), c_int(num_kv_heads),
+            c_int(page_size), c_int(window or 0), c_int(chunk or 0), c_int(1 if sink else 0), c_float(scale), c_float(lam),
+            c_int(1 if head_norm else 0), c_float(eps), c_float(out_scale), c_int(max(q_lens)), c_int(step.max_kv_len),
+            c_int(1 if any(n == 1 for n in q_lens) else 0), c_int(1 if any(n > 1 for n in q_lens) else 0), _ptr(scratch),
+            c_long(floats), _stream()))
+        return
     lib = variants()
     _check(lib, lib.coheryn_attention_maps(
         _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache), c_int(_code(q)),
