@@ -25,7 +25,9 @@ decoding at batch 8.  ``--workload chat-1.5b`` is this repository's own: 256 sho
 that requests end and begin all the time and many steps carry a new prompt beside decoded tokens,
 which no graph replays: it measures what such steps cost the host.  ``--workload kapudra`` measures the Kapudra design
 (matrix-memory layers and attention beside a gated delta rule) at two layer sizes beside Qwen2 at equal sizes: prefill and
-decode through the step function, and the mixers' kernels alone.
+decode through the step function, and the mixers' kernels alone.  ``--workload tutunex`` does the same for the Tutunex
+design (differential attention over chunks, attention with a sink beside a gated delta rule, norms before and after each
+sub-layer), its kernels beside the like kernels of the other models.
 """
 from __future__ import annotations
 
@@ -253,17 +255,16 @@ def kapudra_config(z):
             "logit_scale": 1.0, "logit_softcap": 30.0, "layers": [kinds[i % 4] for i in range(z["layers"])]}
 
 
-def kapudra_workload(args) -> int:
-    """Prefill and decode throughput of Kapudra and of Qwen2 at equal sizes through the step function (CUDA events around
-    the steps, inputs from pinned host memory as every step has them), and the mixers' kernels alone with their share of
-    the roofline.  One JSON line."""
+def model_bench_tools(args):
+    """What the per-design workloads share: peaks, a timer of single kernels with L2 flushed before each run, prefill and
+    decode of a model through the step function (CUDA events around the steps, inputs from pinned host memory as every step
+    has them), and a step description for kernels that are run alone."""
+    import types
     import numpy as np
     import torch
 
     from coheryn_ai_studio_b200 import ops
     from coheryn_ai_studio_b200.cache import CacheManager
-    from coheryn_ai_studio_b200.config import Qwen2Config
-    from coheryn_ai_studio_b200.config.kapudra import KapudraConfig
     from coheryn_ai_studio_b200.engine import StepEntry, StepRunner, random_model_on_device
 
     pk = peaks()
@@ -334,6 +335,27 @@ def kapudra_workload(args) -> int:
             q_lens=list(lengths), kv_lens=t([s + n for s, n in zip(starts, lengths)]), max_q_len=max(lengths),
             max_kv_len=max(s + n for s, n in zip(starts, lengths)), prior_positions_settled=True, block_tables=[tables])
         return st
+
+    return types.SimpleNamespace(pk=pk, hbm=hbm, flops_peak=flops_peak, dev=dev, tokens=tokens, batch=batch, context=context,
+                                 steps=steps, rng=rng, timed=timed, run_model=run_model, step_like=step_like)
+
+
+def kapudra_workload(args) -> int:
+    """Prefill and decode throughput of Kapudra and of Qwen2 at equal sizes through the step function (CUDA events around
+    the steps, inputs from pinned host memory as every step has them), and the mixers' kernels alone with their share of
+    the roofline.  One JSON line."""
+    import numpy as np
+    import torch
+
+    from coheryn_ai_studio_b200 import ops
+    from coheryn_ai_studio_b200.config import Qwen2Config
+    from coheryn_ai_studio_b200.config.kapudra import KapudraConfig
+    from coheryn_ai_studio_b200.engine import random_model_on_device
+
+    tools = model_bench_tools(args)
+    pk, hbm, flops_peak, dev = tools.pk, tools.hbm, tools.flops_peak, tools.dev
+    tokens, batch, context, steps = tools.tokens, tools.batch, tools.context, tools.steps
+    timed, run_model, step_like = tools.timed, tools.run_model, tools.step_like
 
     def kernels(z):
         """The mixers' kernels alone, prompt (one request of ``tokens``) and decode (``batch`` requests at ``context``)."""
@@ -414,6 +436,173 @@ def kapudra_workload(args) -> int:
     return 0
 
 
+# Tutunex at layer sizes that resemble a real model's (random weights), beside Qwen2 at the same width, feed-forward
+# size, head counts and number of layers.  Eight layers: differential attention over chunks, attention with a sink beside
+# a gated delta rule, differential attention on the first layer's keys and values, differential attention; twice.
+TUTUNEX_SIZES = {
+    "1.5b-like": dict(width=1536, ff=4096, heads=12, kv_heads=2, map_dim=64, vdim=128, chunk=1024, side_dim=128, state_heads=12,
+                      state_dim=128, vocab=32000, layers=8),
+    "3b-like": dict(width=2560, ff=6912, heads=20, kv_heads=4, map_dim=64, vdim=128, chunk=2048, side_dim=128, state_heads=16,
+                    state_dim=128, vocab=32000, layers=8),
+}
+
+
+def tutunex_config(z):
+    rot = {"dims": z["map_dim"], "base": 500000.0, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}
+
+    def attention(kv_from=None):
+        m = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["map_dim"], "vdim": z["vdim"], "scale": z["map_dim"] ** -0.5,
+             "diff": 0.5, "rot": rot, "mask": {"size": z["chunk"]}}
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return {"type": "attention", "mixer": m, "mlp": {"kind": "dense", "ff": z["ff"], "limit": 7.0}}
+    left = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": z["side_dim"], "vdim": z["side_dim"], "scale": z["side_dim"] ** -0.5}
+    right = {"heads": z["state_heads"], "kv_heads": z["state_heads"], "dim": z["state_dim"], "vdim": z["state_dim"], "conv": 4}
+    par = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": {"kind": "dense", "ff": z["ff"], "limit": 7.0}}
+    layers = []
+    for i in range(z["layers"]):
+        k = i % 4
+        layers.append(par if k == 1 else attention(kv_from=i - 2 if k == 2 else None))
+    return {"architecture": "Tutunex", "vocab": z["vocab"], "width": z["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "layers": layers}
+
+
+def tutunex_workload(args) -> int:
+    """Prefill and decode throughput of Tutunex and of Qwen2 at equal sizes through the step function, and the design's own
+    kernels alone beside the like kernels of the other models, each with its share of the roofline.  One JSON line."""
+    import numpy as np
+    import torch
+
+    from coheryn_ai_studio_b200 import ops
+    from coheryn_ai_studio_b200.config import Qwen2Config
+    from coheryn_ai_studio_b200.config.tutunex import TutunexConfig
+    from coheryn_ai_studio_b200.engine import random_model_on_device
+    from coheryn_ai_studio_b200.parts.base import Runtime
+    from coheryn_ai_studio_b200.parts.position import ComputedRope, RotateHalfRope
+
+    tools = model_bench_tools(args)
+    pk, hbm, flops_peak, dev = tools.pk, tools.hbm, tools.flops_peak, tools.dev
+    tokens, batch, context = tools.tokens, tools.batch, tools.context
+    timed, step_like = tools.timed, tools.step_like
+
+    def kernels(z):
+        out = {}
+        H, G, dm, dv, chunk, page, W = z["heads"], z["kv_heads"], z["map_dim"], z["vdim"], z["chunk"], args.page_size, z["width"]
+        ds = z["side_dim"]
+        f = lambda *shape: torch.randn(shape, device=dev)
+        b16 = lambda *shape: f(*shape).to(torch.bfloat16)
+        for name, lengths, starts in (("prefill", [tokens], [0]), ("decode", [1] * batch, [context] * batch)):
+            B, T = len(lengths), sum(lengths)
+            per = -(-max(s + n for s, n in zip(starts, lengths)) // page)
+            tables = torch.arange(B * per, dtype=torch.int32, device=dev).view(B, per)
+            st = step_like(lengths, starts, tables)
+            st.slots = [(tables[st.token_req.long(), (st.positions // page).long()] * page + st.positions % page).to(torch.int32)]
+            rows = [p for s, n in zip(starts, lengths) for p in range(s, s + n)]
+
+            def report(label, fn, keys, qk, vd, kv_row_bytes, kv_positions):
+                ms = timed(fn)
+                fl = 2.0 * H * (qk + vd) * keys
+                by = kv_row_bytes * G * kv_positions + 2.0 * T * H * (qk + vd)
+                out[f"{name}.{label}"] = {"ms": round(ms, 4), "tflops": round(fl / ms / 1e9, 1), "of_bf16_peak": round(fl / (ms / 1e3) / flops_peak, 4),
+                                          "of_hbm": round(by / (ms / 1e3) / hbm, 4)}
+            # differential attention over chunks, and Qwen2's attention with a window of the chunk's size at the same head size
+            kc, vc = b16(B * per + 1, G, page, 2 * dm), b16(B * per + 1, G, page, dv)
+            q, o = b16(T, H * 2 * dm), torch.empty((T, H * dv), dtype=torch.bfloat16, device=dev)
+            seen_chunk = sum(p % chunk + 1 for p in rows)
+            held_chunk = sum(min(chunk, s + n) if n > 1 else (s + n - 1) % chunk + 1 for s, n in zip(starts, lengths))
+            report("attention_two_maps_chunk", lambda: ops.attention_maps(q, o, kc, vc, st, 0, H, G, dm, dv, 2, page, None, chunk, False,
+                                                                          dm ** -0.5, 0.6, True, 1e-6, 0.5),
+                   seen_chunk, 2 * dm, dv, 2.0 * (2 * dm + dv), held_chunk)
+            hd = 2 * dm
+            kq, vq = b16(B * per + 1, G, page, hd), b16(B * per + 1, G, page, hd)
+            qq, oq = b16(T, H * hd), torch.empty((T, H * hd), dtype=torch.bfloat16, device=dev)
+            seen_window = sum(min(chunk, p + 1) for p in rows)
+            report("qwen2_attention_window", lambda: ops.attention_rows(qq, oq, kq, vq, tables, st.token_req, st.positions, H, G, hd, page, chunk,
+                                                                        hd ** -0.5, cu_q=st.cu_q, kv_lens=st.kv_lens, q_lens=st.q_lens,
+                                                                        max_kv_len=st.max_kv_len),
+                   seen_window, hd, hd, 4.0 * hd, sum(min(chunk, s + n) for s, n in zip(starts, lengths)))
+            # causal attention with a sink, and Qwen2's causal attention
+            ks, vs = b16(B * per + 1, G, page, ds), b16(B * per + 1, G, page, ds)
+            qs, os_ = b16(T, H * ds), torch.empty((T, H * ds), dtype=torch.bfloat16, device=dev)
+            seen_all = sum(p + 1 for p in rows)
+            held_all = sum(s + n for s, n in zip(starts, lengths))
+            report("attention_sink_causal", lambda: ops.attention_maps(qs, os_, ks, vs, st, 0, H, G, ds, ds, 1, page, None, None, True,
+                                                                       ds ** -0.5, 0.0, False, 1e-6, 1.0), seen_all, ds, ds, 4.0 * ds, held_all)
+            report("qwen2_attention_causal", lambda: ops.attention_rows(qs, os_, ks, vs, tables, st.token_req, st.positions, H, G, ds, page, None,
+                                                                        ds ** -0.5, cu_q=st.cu_q, kv_lens=st.kv_lens, q_lens=st.q_lens,
+                                                                        max_kv_len=st.max_kv_len), seen_all, ds, ds, 4.0 * ds, held_all)
+
+            def elementwise(label, fn, by):
+                ms = timed(fn)
+                out[f"{name}.{label}"] = {"ms": round(ms, 4), "of_hbm": round(by / (ms / 1e3) / hbm, 4)}
+            # queries and keys rotated by computed angles into the cache, and Qwen2's rotation by table
+            proj = f(T, (H * 2 * dm) + (G * 2 * dm) + G * dv)
+            nq, nk = H * 2 * dm, G * 2 * dm
+            rope = ComputedRope(Runtime(torch.bfloat16, dev), dm, 500000.0, {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0})
+            pairs, amp = rope.frequency_pairs(), rope.amplitude
+            elementwise("rotate_computed_and_cache_write",
+                        lambda: ops.unit_norm_rope_kv_write(proj[:, :nq], proj[:, nq:nq + nk], proj[:, nq + nk:], None, None, 1e-6, st.positions, pairs,
+                                                            dm, amp, st.slots[0], kc, vc, 2 * H, 2 * G, G, dm, dv, page, torch.bfloat16),
+                        proj.numel() * 4.0 + proj.numel() * 2.0)
+            table = RotateHalfRope(Runtime(torch.bfloat16, dev), hd, hd, 1e6, context + tokens + 8).cos_sin()
+            qkv = b16(T, (H + 2 * G) * hd)
+            elementwise("qwen2_rotate_by_table_and_cache_write",
+                        lambda: ops.rope_kv_write(qkv, st.positions, table, st.slots[0], kq, vq, H, G, hd, hd, page),
+                        qkv.numel() * 2.0 + (H + 2 * G) * hd * T * 2.0)
+            # the residual add of a normalised summand with the next norm, and the plain add with the norm
+            resid, y2, w1, w2 = f(T, W), f(2, T, W), f(W), f(W)
+            wi, h = f(2, W), torch.empty((T, W), dtype=torch.bfloat16, device=dev)
+            elementwise("add_normalised_and_norm", lambda: ops.add_normed_rmsnorm(resid, y2[0], None, 1.0, w1, w2, 1e-6, h), T * W * (4 + 8 + 2.0))
+            elementwise("add_two_normalised_and_norm", lambda: ops.add_normed_rmsnorm(resid, y2, wi, 0.5, w1, w2, 1e-6, h), T * W * (8 + 8 + 2.0))
+            yb = b16(T, W)
+            elementwise("qwen2_add_and_norm", lambda: ops.add_rmsnorm(resid, yb, w2, 1e-6, h), T * W * (2 + 8 + 2.0))
+            # the delta rule with one decay per head and a SiLU gate, and Kapudra's with a decay per head and key channel
+            heads, dk = z["state_heads"], z["state_dim"]
+            qkvs = f(T, 3 * heads * dk)
+            gate, outb = f(T, heads * dk), torch.empty((T, heads * dk), dtype=torch.bfloat16, device=dev)
+            state = torch.zeros((B, heads * dk * dk), device=dev)
+            beta, pre1, preC, bias1, biasC, rate, wn = f(T, heads), f(T, heads), f(T, heads * dk), f(heads), f(heads * dk), f(heads) * 0.1, f(dk)
+            for label, pre, bias, per_channel, act in (("delta_rule_decay_per_head", pre1, bias1, False, "silu"),
+                                                       ("kapudra_delta_rule_decay_per_channel", preC, biasC, True, "sigmoid")):
+                fn = lambda: ops.gated_delta_scan(qkvs[:, :heads * dk], qkvs[:, heads * dk:2 * heads * dk], qkvs[:, 2 * heads * dk:], beta, pre, bias,
+                                                  rate, state, st, heads, heads, dk, dk, outb, wn, gate, 1e-6, decay_per_channel=per_channel,
+                                                  gate_activation=act)
+                ms = timed(fn)
+                by = 2.0 * state.numel() * 4 + qkvs.numel() * 4 + gate.numel() * 4 + outb.numel() * 2
+                fl = 8.0 * heads * dk * dk * T
+                out[f"{name}.{label}"] = {"ms": round(ms, 4), "of_hbm": round(by / (ms / 1e3) / hbm, 4),
+                                          "of_fp32_fma_peak": round(fl / (ms / 1e3) / 75e12, 4)}
+        return out
+
+    sampler = ClockSampler()
+    sampler.start()
+    t0 = time.time()
+    results = {}
+    chosen = [n for n in TUTUNEX_SIZES if not args.sizes or n in args.sizes.split(",")]
+    for name in chosen:
+        z = TUTUNEX_SIZES[name]
+        entry = {}
+        model = random_model_on_device(TutunexConfig.from_dict(tutunex_config(z)), seed=0, dtype="bfloat16", device="cuda:0")
+        entry["tutunex"] = tools.run_model(model, z["vocab"])
+        del model
+        torch.cuda.empty_cache()
+        qcfg = Qwen2Config(vocab_size=z["vocab"], hidden_size=z["width"], intermediate_size=z["ff"], num_hidden_layers=z["layers"],
+                           num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=2 * z["map_dim"],
+                           max_position_embeddings=32768, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=False)
+        model = random_model_on_device(qcfg, seed=0, dtype="bfloat16", device="cuda:0")
+        entry["qwen2_equal_size"] = tools.run_model(model, z["vocab"])
+        del model
+        torch.cuda.empty_cache()
+        entry["kernels"] = kernels(z)
+        results[name] = entry
+    clocks = ClockSampler.summary(sampler.window(t0, time.time()))
+    sampler.stop()
+    print(json.dumps({"workload": "tutunex", "dtype": "bf16", "data": "synthetic", "prefill_tokens": tokens, "decode_batch": batch,
+                      "decode_context": context, "decode_steps": tools.steps, "peaks": pk, "clocks": clocks,
+                      "l2": "flushed before each timed kernel", "gpu_launches": ops.total_launch_count(), "sizes": results}))
+    return 0
+
+
 def timeline(args, make_engine, StepEntry, ops, torch) -> int:
     """Where a decode step's time goes, kernel by kernel, measured inside graph-replayed steps (the
     kernels overlap through programmatic dependent launch, so a kernel's own duration says little):
@@ -481,9 +670,9 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=16)
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points")
     ap.add_argument("--no-graphs", action="store_true")
-    ap.add_argument("--workload", default="decode", choices=["decode", "serving-7b", "long-14b", "chat-1.5b", "kapudra"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "serving-7b", "long-14b", "chat-1.5b", "kapudra", "tutunex"],
                     help="decode: the contract's line (default); the others: see the header")
-    ap.add_argument("--sizes", default="", help="--workload kapudra: which of its sizes (comma separated; default all)")
+    ap.add_argument("--sizes", default="", help="--workload kapudra / tutunex: which of its sizes (comma separated; default all)")
     ap.add_argument("--timeline-raw", action="store_true", help="with --timeline: also every kernel's start and end")
     ap.add_argument("--timeline", action="store_true",
                     help="instead of the benchmark: the kernels of one graph-replayed decode step with their times "
@@ -502,6 +691,8 @@ def main() -> int:
         args.warmup = 3
     if args.workload == "kapudra":
         return kapudra_workload(args)
+    if args.workload == "tutunex":
+        return tutunex_workload(args)
     if args.workload != "decode":
         return other_workload(args)
 

@@ -13,7 +13,7 @@
 // cost one accumulator, and the difference of the maps is taken before anything is rounded.
 //
 // Decoding (`maps_decode_kernel` + `maps_combine_kernel`): the rows of a tile are the query heads of ONE key/value
-// head for one token, the visible keys are cut into at most eight splits at absolute multiples of the split size,
+// head for one token, the visible keys are cut into at most sixteen splits at absolute multiples of the split size,
 // each of a CTA's four warps takes a quarter of a split (an online softmax over its tiles, one map after the other)
 // and leaves (maximum, sum, unnormalised output) per head and map; a second kernel merges the parts in order, adds
 // the sink, takes the difference of the maps, normalises and writes.
@@ -34,9 +34,14 @@ static_assert(MAPS == 1 || MAPS == 2, "one score map or two");
 constexpr int KROW = MAPS * DK;                  // channels of a key row (and of a query head)
 constexpr int KS = KROW + 8, VS = DV + 8;        // padded row strides in shared memory: an odd number of 16-byte units
 constexpr int BM = 64, WARPS = 4;
+#ifdef CO_MAPS_BN
+constexpr int BN = CO_MAPS_BN;                   // a measuring switch: keys per tile
+#else
 constexpr int BN = (DV > 128 || KROW > 128) ? 32 : 64;
+#endif
+static_assert(BN == 32 || BN == 64, "key tiles of 32 or 64 positions");
 constexpr int NT = BN / 8, OT = DV / 8;
-constexpr int MAX_SPLITS = 8;
+constexpr int MAX_SPLITS = 16;
 typedef __nv_bfloat16 bf16;
 
 struct MapsArgs {
@@ -86,21 +91,40 @@ __device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
   return f;
 }
 
-// Rows `key0 .. key0 + n - 1` of a request's keys (and values) into shared memory by `threads` threads; a position
-// at or beyond `kv_len`, or on a page that is gone, becomes zeros.
-__device__ __forceinline__ void load_keys(bf16* ks, bf16* vs, const MapsArgs& A, const int* table, int kvh, int key0, int n,
-                                          int kv_len, int tid, int threads) {
+// 2^x by the hardware's approximation (two units in the last place; 2^-inf = 0).
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Rows `key0 .. key0 + BN - 1` of a request's keys (and values) into shared memory by THREADS threads; a position
+// at or beyond `kv_len`, or on a page that is gone, becomes zeros.  A row is looked up once by the threads that share it.
+template <int THREADS>
+__device__ __forceinline__ void load_keys(bf16* ks, bf16* vs, const MapsArgs& A, const int* table, int kvh, int key0,
+                                          int kv_len, int tid) {
   constexpr int KC = KROW / 8, VC = DV / 8;
-  const int per_row = KC + (vs ? VC : 0);
-  for (int c = tid; c < n * per_row; c += threads) {
-    const int row = c / per_row, ch = c % per_row;
+  constexpr int TPR = THREADS >= BN ? THREADS / BN : 1;        // threads per row
+  constexpr int ROWS = THREADS / TPR;                          // rows per round
+  const int sub = tid % TPR;
+#pragma unroll
+  for (int row = tid / TPR; row < BN; row += ROWS) {
     const int j = key0 + row;
     int page = -1;
     if (j < kv_len) page = table[j / A.page_size];
     const bool ok = page >= 0;
+    const int bytes = ok ? 16 : 0;
     const size_t at = ok ? ((size_t)page * A.nkv + kvh) * A.page_size + (size_t)(j % A.page_size) : 0;
-    if (ch < KC) cp_async16(ks + row * KS + ch * 8, A.k_cache + at * KROW + ch * 8, ok ? 16 : 0);
-    else cp_async16(vs + row * VS + (ch - KC) * 8, A.v_cache + at * DV + (ch - KC) * 8, ok ? 16 : 0);
+    const bf16* ksrc = A.k_cache + at * KROW;
+    bf16* kdst = ks + row * KS;
+#pragma unroll
+    for (int ch = sub; ch < KC; ch += TPR) cp_async16(kdst + ch * 8, ksrc + ch * 8, bytes);
+    if (vs) {
+      const bf16* vsrc = A.v_cache + at * DV;
+      bf16* vdst = vs + row * VS;
+#pragma unroll
+      for (int ch = sub; ch < VC; ch += TPR) cp_async16(vdst + ch * 8, vsrc + ch * 8, bytes);
+    }
   }
 }
 
@@ -159,6 +183,13 @@ __device__ __forceinline__ void mask_scale(float (&s)[NT][4], int key0, int lane
     }
 }
 
+__device__ __forceinline__ void scale_only(float (&s)[NT][4], float scale_log2) {
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[nt][e] *= scale_log2;
+}
+
 // ---------------------------------------------------------------------------------
 // Prompt portions.  grid: (row tiles of the longest request, requests, query heads).
 // ---------------------------------------------------------------------------------
@@ -169,8 +200,9 @@ __global__ void __launch_bounds__(WARPS * 32) maps_tiles_kernel(MapsArgs A) {
   bf16* vs = ks + 2 * BN * KS;                         // [2][BN][VS]
   co_pdl_launch_dependents();
   co_pdl_wait();
-  const int tile = blockIdx.x, r = blockIdx.y, h = blockIdx.z;
+  const int r = blockIdx.y, h = blockIdx.z;
   const int q0 = A.cu_q[r], q_len = A.cu_q[r + 1] - q0, kv_len = A.kv_lens[r];
+  const int tile = (int)gridDim.x - 1 - (int)blockIdx.x;          // later rows see more keys: their CTAs start first
   if (tile * BM >= q_len || (A.skip_single && q_len == 1)) return;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int kvh = h / (A.nh / A.nkv);
@@ -191,24 +223,33 @@ __global__ void __launch_bounds__(WARPS * 32) maps_tiles_kernel(MapsArgs A) {
     first[i] = row < rows ? first_visible(pos[i], A.window, A.chunk) : 0;
   }
   const bf16* qw = qs + warp * 16 * KS;
+  // what the warp's rows see together: a tile none of them sees is skipped, one all of them see whole needs no mask
+  const bool whole_warp = warp * 16 + 15 < rows;
+  const int wp_lo = pos_lo + warp * 16, wp_hi = min(pos_hi, wp_lo + 15);
+  const int wf_lo = first_visible(min(wp_lo, pos_hi), A.window, A.chunk), wf_hi = first_visible(wp_hi, A.window, A.chunk);
 
   // pass 1: maximum and sum of every row, per map
   float mx[MAPS][2], sum[MAPS][2];
 #pragma unroll
   for (int m = 0; m < MAPS; ++m) { mx[m][0] = mx[m][1] = -INFINITY; sum[m][0] = sum[m][1] = 0.f; }
-  load_keys(ks, nullptr, A, table, kvh, t_lo * BN, BN, kv_len, tid, WARPS * 32);
+  load_keys<WARPS * 32>(ks, nullptr, A, table, kvh, t_lo * BN, kv_len, tid);
   cp_commit();
   for (int i = 0; i < n_tiles; ++i) {
-    if (i + 1 < n_tiles) load_keys(ks + ((i + 1) & 1) * BN * KS, nullptr, A, table, kvh, (t_lo + i + 1) * BN, BN, kv_len, tid, WARPS * 32);
+    if (i + 1 < n_tiles) load_keys<WARPS * 32>(ks + ((i + 1) & 1) * BN * KS, nullptr, A, table, kvh, (t_lo + i + 1) * BN, kv_len, tid);
     cp_commit();
     cp_wait<1>();
     __syncthreads();
     const bf16* kt = ks + (i & 1) * BN * KS;
+    const int key0 = (t_lo + i) * BN;
+    const bool unseen = warp * 16 >= rows || key0 > wp_hi || key0 + BN - 1 < wf_lo;
+    const bool open = whole_warp && key0 >= wf_hi && key0 + BN - 1 <= wp_lo;
 #pragma unroll
     for (int m = 0; m < MAPS; ++m) {
+      if (unseen) break;
       float s[NT][4];
       scores(s, qw, kt, m, lane);
-      mask_scale(s, (t_lo + i) * BN, lane, pos, first, A.scale_log2);
+      if (open) scale_only(s, A.scale_log2);
+      else mask_scale(s, key0, lane, pos, first, A.scale_log2);
 #pragma unroll
       for (int rr = 0; rr < 2; ++rr) {
         float tm = -INFINITY;
@@ -219,8 +260,8 @@ __global__ void __launch_bounds__(WARPS * 32) maps_tiles_kernel(MapsArgs A) {
         if (mn != -INFINITY) {
           float add = 0.f;
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) add += exp2f(s[nt][2 * rr] - mn) + exp2f(s[nt][2 * rr + 1] - mn);
-          sum[m][rr] = sum[m][rr] * exp2f(mx[m][rr] - mn) + add;     // exp2f(-inf) = 0 the first time
+          for (int nt = 0; nt < NT; ++nt) add += ex2(s[nt][2 * rr] - mn) + ex2(s[nt][2 * rr + 1] - mn);
+          sum[m][rr] = sum[m][rr] * ex2(mx[m][rr] - mn) + add;     // ex2(-inf) = 0 the first time
           mx[m][rr] = mn;
         }
       }
@@ -235,7 +276,7 @@ __global__ void __launch_bounds__(WARPS * 32) maps_tiles_kernel(MapsArgs A) {
       float l = quad_sum(sum[m][rr]), M = mx[m][rr];
       if (A.sink && M != -INFINITY) {               // one more term exp(0) that carries no value
         const float M2 = fmaxf(M, 0.f);
-        l = l * exp2f(M - M2) + exp2f(-M2);
+        l = l * ex2(M - M2) + ex2(-M2);
         M = M2;
       }
       if (M == -INFINITY) { M = 0.f; inv[m][rr] = 0.f; }      // a row beyond the portion
@@ -247,34 +288,41 @@ __global__ void __launch_bounds__(WARPS * 32) maps_tiles_kernel(MapsArgs A) {
   float o[OT][4];
 #pragma unroll
   for (int nt = 0; nt < OT; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
-  load_keys(ks, vs, A, table, kvh, t_lo * BN, BN, kv_len, tid, WARPS * 32);
+  load_keys<WARPS * 32>(ks, vs, A, table, kvh, t_lo * BN, kv_len, tid);
   cp_commit();
   for (int i = 0; i < n_tiles; ++i) {
     if (i + 1 < n_tiles)
-      load_keys(ks + ((i + 1) & 1) * BN * KS, vs + ((i + 1) & 1) * BN * VS, A, table, kvh, (t_lo + i + 1) * BN, BN, kv_len, tid, WARPS * 32);
+      load_keys<WARPS * 32>(ks + ((i + 1) & 1) * BN * KS, vs + ((i + 1) & 1) * BN * VS, A, table, kvh, (t_lo + i + 1) * BN, kv_len, tid);
     cp_commit();
     cp_wait<1>();
     __syncthreads();
     const bf16* kt = ks + (i & 1) * BN * KS;
+    const int key0 = (t_lo + i) * BN;
+    const bool unseen = warp * 16 >= rows || key0 > wp_hi || key0 + BN - 1 < wf_lo;
+    const bool open = whole_warp && key0 >= wf_hi && key0 + BN - 1 <= wp_lo;
+    if (!unseen) {
     float w[NT][4];
     {
       float s[NT][4];
       scores(s, qw, kt, 0, lane);
-      mask_scale(s, (t_lo + i) * BN, lane, pos, first, A.scale_log2);
+      if (open) scale_only(s, A.scale_log2);
+      else mask_scale(s, key0, lane, pos, first, A.scale_log2);
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) w[nt][e] = exp2f(s[nt][e] - mx[0][e >> 1]) * inv[0][e >> 1];
+        for (int e = 0; e < 4; ++e) w[nt][e] = ex2(s[nt][e] - mx[0][e >> 1]) * inv[0][e >> 1];
       if (MAPS == 2) {
         scores(s, qw, kt, MAPS - 1, lane);
-        mask_scale(s, (t_lo + i) * BN, lane, pos, first, A.scale_log2);
+        if (open) scale_only(s, A.scale_log2);
+        else mask_scale(s, key0, lane, pos, first, A.scale_log2);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-          for (int e = 0; e < 4; ++e) w[nt][e] -= A.lambda * (exp2f(s[nt][e] - mx[MAPS - 1][e >> 1]) * inv[MAPS - 1][e >> 1]);
+          for (int e = 0; e < 4; ++e) w[nt][e] -= A.lambda * (ex2(s[nt][e] - mx[MAPS - 1][e >> 1]) * inv[MAPS - 1][e >> 1]);
       }
     }
     weights_times_values(o, w, vs + (i & 1) * BN * VS, lane);
+    }
     __syncthreads();
   }
 #pragma unroll
@@ -298,9 +346,9 @@ __global__ void __launch_bounds__(WARPS * 32) maps_tiles_kernel(MapsArgs A) {
 
 // ---------------------------------------------------------------------------------
 // Decoding: requests that bring ONE token.  grid: (requests, kv heads, splits).  A part = (split, warp).
-// scratch: [request][query head][map][MAX_SPLITS * WARPS parts][DV + 2] = (output[DV], maximum, sum).
+// scratch: [request][query head][map][splits * WARPS parts][DV + 2] = (output[DV], maximum, sum).
 // ---------------------------------------------------------------------------------
-__global__ void __launch_bounds__(WARPS * 32) maps_decode_kernel(MapsArgs A, float* __restrict__ scratch, int split_keys) {
+__global__ void __launch_bounds__(WARPS * 32) maps_decode_kernel(MapsArgs A, float* __restrict__ scratch, int split_keys, int n_splits) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);        // [16][KS]: the query heads of the kv head, then zero rows
   bf16* kall = qs + 16 * KS;                           // [WARPS][BN][KS]
@@ -322,25 +370,29 @@ __global__ void __launch_bounds__(WARPS * 32) maps_decode_kernel(MapsArgs A, flo
     cp_async16(qs + row * KS + ch * 8, A.q + (size_t)q0 * A.ldq + (size_t)(kvh * group + (ok ? row : 0)) * KROW + ch * 8, ok ? 16 : 0);
   }
   cp_commit();
-  cp_wait<0>();
-  __syncthreads();
   bf16* kw = kall + warp * BN * KS;
   bf16* vw = vall + warp * BN * VS;
   const int quarter = split_keys / WARPS;                         // a multiple of BN
   const int w_lo = key_lo + warp * quarter, w_hi = min(w_lo + quarter, p + 1);
   const int pos[2] = {(lane >> 2) < group ? p : -1, (lane >> 2) + 8 < group ? p : -1};
   const int first[2] = {f, f};
+  if (w_lo < w_hi) load_keys<32>(kw, vw, A, table, kvh, w_lo, p + 1, lane);     // in flight with the queries
+  cp_commit();
+  cp_wait<0>();
+  __syncthreads();
   for (int m = 0; m < MAPS; ++m) {
     float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f};
     float o[OT][4];
 #pragma unroll
     for (int nt = 0; nt < OT; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
     for (int key0 = w_lo; key0 < w_hi; key0 += BN) {
-      __syncwarp();
-      load_keys(kw, vw, A, table, kvh, key0, BN, p + 1, lane, 32);
-      cp_commit();
-      cp_wait<0>();
-      __syncwarp();
+      if (key0 != w_lo || (m > 0 && w_lo + BN < w_hi)) {       // the first tile is there already, unless a later one took its place
+        __syncwarp();
+        load_keys<32>(kw, vw, A, table, kvh, key0, p + 1, lane);
+        cp_commit();
+        cp_wait<0>();
+        __syncwarp();
+      }
       float s[NT][4];
       scores(s, qs, kw, m, lane);
       mask_scale(s, key0, lane, pos, first, A.scale_log2);
@@ -352,12 +404,12 @@ __global__ void __launch_bounds__(WARPS * 32) maps_decode_kernel(MapsArgs A, flo
         tm = quad_max(tm);
         const float mn = fmaxf(mx[rr], tm);
         const float safe = mn == -INFINITY ? 0.f : mn;
-        const float corr = exp2f(mx[rr] - safe);                  // 0 the first time
+        const float corr = ex2(mx[rr] - safe);                  // 0 the first time
         float add = 0.f;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          s[nt][2 * rr] = exp2f(s[nt][2 * rr] - safe);
-          s[nt][2 * rr + 1] = exp2f(s[nt][2 * rr + 1] - safe);
+          s[nt][2 * rr] = ex2(s[nt][2 * rr] - safe);
+          s[nt][2 * rr + 1] = ex2(s[nt][2 * rr + 1] - safe);
           add += s[nt][2 * rr] + s[nt][2 * rr + 1];
           }
         sum[rr] = sum[rr] * corr + add;
@@ -372,7 +424,7 @@ __global__ void __launch_bounds__(WARPS * 32) maps_decode_kernel(MapsArgs A, flo
       const int row = (lane >> 2) + 8 * rr;
       const float l = quad_sum(sum[rr]);
       if (row < group) {
-        float* part = scratch + ((((size_t)r * A.nh + kvh * group + row) * MAPS + m) * (MAX_SPLITS * WARPS) + split * WARPS + warp) * (DV + 2);
+        float* part = scratch + ((((size_t)r * A.nh + kvh * group + row) * MAPS + m) * (n_splits * WARPS) + split * WARPS + warp) * (DV + 2);
 #pragma unroll
         for (int nt = 0; nt < OT; ++nt) {
           part[nt * 8 + 2 * (lane & 3)] = o[nt][2 * rr];
@@ -385,7 +437,7 @@ __global__ void __launch_bounds__(WARPS * 32) maps_decode_kernel(MapsArgs A, flo
 }
 
 // grid: (requests, query heads); DV threads are enough, any block size works.
-__global__ void __launch_bounds__(128) maps_combine_kernel(MapsArgs A, const float* __restrict__ scratch, int split_keys) {
+__global__ void __launch_bounds__(128) maps_combine_kernel(MapsArgs A, const float* __restrict__ scratch, int split_keys, int n_splits) {
   __shared__ float red[33];
   co_pdl_launch_dependents();
   co_pdl_wait();
@@ -398,16 +450,16 @@ __global__ void __launch_bounds__(128) maps_combine_kernel(MapsArgs A, const flo
 #pragma unroll
   for (int i = 0; i < (DV + 127) / 128; ++i) acc[i] = 0.f;
   for (int m = 0; m < MAPS; ++m) {
-    const float* parts = scratch + (((size_t)r * A.nh + h) * MAPS + m) * (MAX_SPLITS * WARPS) * (DV + 2);
+    const float* parts = scratch + (((size_t)r * A.nh + h) * MAPS + m) * (n_splits * WARPS) * (DV + 2);
     float M = A.sink ? 0.f : -INFINITY;
     for (int i = 0; i < n_parts; ++i) M = fmaxf(M, parts[i * (DV + 2) + DV]);
-    float L = A.sink ? exp2f(-M) : 0.f;
-    for (int i = 0; i < n_parts; ++i) L += parts[i * (DV + 2) + DV + 1] * exp2f(parts[i * (DV + 2) + DV] - M);
+    float L = A.sink ? ex2(-M) : 0.f;
+    for (int i = 0; i < n_parts; ++i) L += parts[i * (DV + 2) + DV + 1] * ex2(parts[i * (DV + 2) + DV] - M);
     const float coef = (m == 0 ? 1.0f : -A.lambda) / L;
     int n = 0;
     for (int d = threadIdx.x; d < DV; d += blockDim.x, ++n) {
       float a = 0.f;
-      for (int i = 0; i < n_parts; ++i) a += parts[i * (DV + 2) + d] * exp2f(parts[i * (DV + 2) + DV] - M);
+      for (int i = 0; i < n_parts; ++i) a += parts[i * (DV + 2) + d] * ex2(parts[i * (DV + 2) + DV] - M);
       acc[n] += coef * a;
     }
   }
@@ -427,8 +479,27 @@ __global__ void __launch_bounds__(128) maps_combine_kernel(MapsArgs A, const flo
 
 CO_EXPORT int coheryn_maps_shape(int* dk, int* dv, int* maps) { *dk = DK; *dv = DV; *maps = MAPS; return 0; }
 
-// Floats of scratch that the decode kernels need for `B` requests.
-CO_EXPORT long coheryn_maps_scratch_floats(int B, int nh) { return (long)B * nh * MAPS * MAX_SPLITS * WARPS * (DV + 2); }
+// How the keys a decoded row can see are cut: the keys per split (a multiple of what a CTA's warps take in one round, cut at
+// absolute multiples of itself) and the most splits a row then has (its keys may straddle one boundary more than their
+// number fills).
+static void decode_plan(int max_kv_len, int window, int chunk, int* split_keys, int* n_splits) {
+  int visible = max_kv_len;
+  if (chunk > 0 && chunk < visible) visible = chunk;
+  if (window > 0 && window < visible) visible = window;
+  const int unit = WARPS * BN;
+  int keys = ((visible + (MAX_SPLITS - 1) - 1) / (MAX_SPLITS - 1) + unit - 1) / unit * unit;
+  if (keys < unit) keys = unit;
+  *split_keys = keys;
+  int n = (visible + keys - 1) / keys + 1;
+  *n_splits = n > MAX_SPLITS ? MAX_SPLITS : n;
+}
+
+// Floats of scratch that the decode kernels need for `B` requests whose longest context is `max_kv_len`.
+CO_EXPORT long coheryn_maps_scratch_floats(int B, int nh, int max_kv_len, int window, int chunk) {
+  int keys, n;
+  decode_plan(max_kv_len, window, chunk, &keys, &n);
+  return (long)B * nh * MAPS * n * WARPS * (DV + 2);
+}
 
 // q [T, nh * maps * dk], out [T, nh * dv]: bfloat16.  The rows of request r are cu_q[r] .. cu_q[r+1], consecutive positions
 // that end at kv_lens[r] - 1.  max_q_len, max_kv_len: host copies of the longest portion and context.  any_single /
@@ -454,19 +525,15 @@ CO_EXPORT int coheryn_attention_maps_bf16(const void* q, long ldq, void* out, lo
     CO_CHECK_LAUNCH("maps_tiles");
   }
   if (decode) {
-    if (scratch_floats < coheryn_maps_scratch_floats(B, nh)) CO_FAIL("attention_maps_bf16: scratch of %ld floats is too small", scratch_floats);
-    int visible = max_kv_len;                              // the most keys a row can see
-    if (chunk > 0 && chunk < visible) visible = chunk;
-    if (window > 0 && window < visible) visible = window;
-    const int unit = WARPS * BN;
-    // a row's keys may straddle one boundary more than their number fills, hence MAX_SPLITS - 1
-    int split_keys = ((visible + (MAX_SPLITS - 1) - 1) / (MAX_SPLITS - 1) + unit - 1) / unit * unit;
-    if (split_keys < unit) split_keys = unit;
+    if (scratch_floats < coheryn_maps_scratch_floats(B, nh, max_kv_len, window, chunk))
+      CO_FAIL("attention_maps_bf16: scratch of %ld floats is too small", scratch_floats);
+    int split_keys, n_splits;
+    decode_plan(max_kv_len, window, chunk, &split_keys, &n_splits);
     const size_t smem = ((size_t)16 * KS + (size_t)WARPS * BN * (KS + VS)) * sizeof(bf16);
     if (smem > 48 * 1024) cudaFuncSetAttribute(maps_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    co_launch(maps_decode_kernel, dim3(B, nkv, MAX_SPLITS), dim3(WARPS * 32), smem, stream, A, scratch, split_keys);
+    co_launch(maps_decode_kernel, dim3(B, nkv, n_splits), dim3(WARPS * 32), smem, stream, A, scratch, split_keys, n_splits);
     CO_CHECK_LAUNCH("maps_decode");
-    co_launch(maps_combine_kernel, dim3(B, nh), dim3(DV >= 128 ? 128 : (DV + 31) / 32 * 32), 0, stream, A, (const float*)scratch, split_keys);
+    co_launch(maps_combine_kernel, dim3(B, nh), dim3(DV >= 128 ? 128 : (DV + 31) / 32 * 32), 0, stream, A, (const float*)scratch, split_keys, n_splits);
     CO_CHECK_LAUNCH("maps_combine");
   }
   return 0;

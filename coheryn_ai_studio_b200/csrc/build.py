@@ -254,8 +254,10 @@ def maps_attention_library(dk: int, dv: int, maps: int) -> ctypes.CDLL:
     if dk % 16 or dv % 16 or not 16 <= dk <= 256 or not 16 <= dv <= 256 or maps not in (1, 2):
         raise BuildError(f"the tensor-core attention with score maps takes head sizes 16..256 in steps of 16 and one or "
                          f"two maps, not ({dk}, {dv}, {maps})")
-    return load_library(f"maps_{dk}_{dv}_{maps}", ["attention_maps_tc.cu", "runtime.cu"],
-                        {"CO_MAPS_DK": dk, "CO_MAPS_DV": dv, "CO_MAPS_N": maps})
+    defines = {"CO_MAPS_DK": dk, "CO_MAPS_DV": dv, "CO_MAPS_N": maps}
+    if os.environ.get("COHERYN_MAPS_BN"):       # a measuring switch: keys per tile (32 or 64)
+        defines["CO_MAPS_BN"] = int(os.environ["COHERYN_MAPS_BN"])
+    return load_library(f"maps_{dk}_{dv}_{maps}", ["attention_maps_tc.cu", "runtime.cu"], defines)
 
 
 def build_all(head_dims: Sequence[int] = (16, 32, 64, 128)) -> List[str]:

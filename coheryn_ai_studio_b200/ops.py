@@ -1202,7 +1202,8 @@ def attention_maps(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_
         lib = maps_attention_lib(dk, dv, maps)
         B = len(q_lens)
         single = any(n == 1 for n in q_lens) and num_heads // num_kv_heads <= 16
-        floats = int(lib.coheryn_maps_scratch_floats(c_int(B), c_int(num_heads))) if single else 0
+        floats = int(lib.coheryn_maps_scratch_floats(c_int(B), c_int(num_heads), c_int(step.max_kv_len), c_int(window or 0),
+                                                     c_int(chunk or 0))) if single else 0
         scratch = torch.empty(floats, dtype=torch.float32, device=q.device) if floats else None
         _check(lib, lib.coheryn_attention_maps_bf16(
             _ptr(q), c_long(q.stride(0)), _ptr(out), c_long(out.stride(0)), _ptr(k_cache), _ptr(v_cache), _ptr(block_tables),
