@@ -37,7 +37,7 @@ constexpr int BM = 64, WARPS = 4;
 #ifdef CO_MAPS_BN
 constexpr int BN = CO_MAPS_BN;                   // a measuring switch: keys per tile
 #else
-constexpr int BN = (DV > 128 || KROW > 128) ? 32 : 64;
+constexpr int BN = 32;      // measured on a B200: tiles of 32 keys with three resident CTAs per SM beat tiles of 64 with two by 12 %
 #endif
 static_assert(BN == 32 || BN == 64, "key tiles of 32 or 64 positions");
 constexpr int NT = BN / 8, OT = DV / 8;
@@ -50,6 +50,7 @@ struct MapsArgs {
   const int* block_tables; int max_blocks;
   const int* cu_q; const int* kv_lens;
   int nh, nkv, page_size, window, chunk, sink, head_norm, skip_single;
+  int table_cache;      // block-table entries a CTA of the prompt kernel may keep in shared memory
   float scale_log2, lambda, eps, out_scale;
 };
 
@@ -193,11 +194,15 @@ __device__ __forceinline__ void scale_only(float (&s)[NT][4], float scale_log2) 
 // ---------------------------------------------------------------------------------
 // Prompt portions.  grid: (row tiles of the longest request, requests, query heads).
 // ---------------------------------------------------------------------------------
-__global__ void __launch_bounds__(WARPS * 32) maps_tiles_kernel(MapsArgs A) {
+#ifndef CO_MAPS_MIN_CTAS
+#define CO_MAPS_MIN_CTAS ((DV <= 128 && KROW <= 128) ? 3 : 1)      // the registers of wider heads allow one
+#endif
+__global__ void __launch_bounds__(WARPS * 32, CO_MAPS_MIN_CTAS) maps_tiles_kernel(MapsArgs A) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* qs = reinterpret_cast<bf16*>(smem_raw);        // [BM][KS]
   bf16* ks = qs + BM * KS;                             // [2][BN][KS]
   bf16* vs = ks + 2 * BN * KS;                         // [2][BN][VS]
+  int* tbl = reinterpret_cast<int*>(vs + 2 * BN * VS); // [table_cache]
   co_pdl_launch_dependents();
   co_pdl_wait();
   const int r = blockIdx.y, h = blockIdx.z;
@@ -215,6 +220,14 @@ __global__ void __launch_bounds__(WARPS * 32) maps_tiles_kernel(MapsArgs A) {
     cp_async16(qs + row * KS + ch * 8, A.q + (size_t)(q0 + tile * BM + (ok ? row : 0)) * A.ldq + (size_t)h * KROW + ch * 8, ok ? 16 : 0);
   }
   const int t_lo = first_visible(pos_lo, A.window, A.chunk) / BN, t_hi = pos_hi / BN, n_tiles = t_hi - t_lo + 1;
+  {   // the pages of the CTA's keys, looked up once: the tile loads then read shared memory
+    const int e0 = (t_lo * BN) / A.page_size, e1 = min(t_hi * BN + BN - 1, kv_len - 1) / A.page_size;
+    if (e1 - e0 + 1 <= A.table_cache) {
+      for (int i = tid; i <= e1 - e0; i += WARPS * 32) tbl[i] = table[e0 + i];
+      __syncthreads();
+      table = tbl - e0;
+    }
+  }
   int pos[2], first[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
@@ -516,10 +529,15 @@ CO_EXPORT int coheryn_attention_maps_bf16(const void* q, long ldq, void* out, lo
   const int group = nh / nkv;
   const bool decode = any_single && group <= 16;
   MapsArgs A{(const bf16*)q, ldq, (bf16*)out, ldo, (const bf16*)k_cache, (const bf16*)v_cache, block_tables, max_blocks, cu_q,
-             kv_lens, nh, nkv, page_size, window, chunk, sink, head_norm, decode ? 1 : 0,
+             kv_lens, nh, nkv, page_size, window, chunk, sink, head_norm, decode ? 1 : 0, 0,
              scale * 1.4426950408889634f, lambda, eps, out_scale};
   if (any_longer || !decode) {
-    const size_t smem = ((size_t)BM * KS + (size_t)2 * BN * KS + (size_t)2 * BN * VS) * sizeof(bf16);
+    int visible = max_kv_len;                              // the most keys a row can see
+    if (chunk > 0 && chunk < visible) visible = chunk;
+    if (window > 0 && window < visible) visible = window;
+    const long entries = ((long)visible + BM + 2 * BN) / page_size + 2;
+    A.table_cache = entries <= 4096 ? (int)entries : 0;    // a longer table is read from global memory
+    const size_t smem = ((size_t)BM * KS + (size_t)2 * BN * KS + (size_t)2 * BN * VS) * sizeof(bf16) + (size_t)A.table_cache * sizeof(int);
     if (smem > 48 * 1024) cudaFuncSetAttribute(maps_tiles_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     co_launch(maps_tiles_kernel, dim3((max_q_len + BM - 1) / BM, B, nh), dim3(WARPS * 32), smem, stream, A);
     CO_CHECK_LAUNCH("maps_tiles");

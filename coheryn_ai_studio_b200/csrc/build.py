@@ -257,6 +257,8 @@ def maps_attention_library(dk: int, dv: int, maps: int) -> ctypes.CDLL:
     defines = {"CO_MAPS_DK": dk, "CO_MAPS_DV": dv, "CO_MAPS_N": maps}
     if os.environ.get("COHERYN_MAPS_BN"):       # a measuring switch: keys per tile (32 or 64)
         defines["CO_MAPS_BN"] = int(os.environ["COHERYN_MAPS_BN"])
+    if os.environ.get("COHERYN_MAPS_MIN_CTAS"):     # ... and the resident CTAs per SM that the prompt kernel's registers must allow
+        defines["CO_MAPS_MIN_CTAS"] = int(os.environ["COHERYN_MAPS_MIN_CTAS"])
     return load_library(f"maps_{dk}_{dv}_{maps}", ["attention_maps_tc.cu", "runtime.cu"], defines)
 
 
