@@ -449,9 +449,12 @@ __global__ void __launch_bounds__(WARPS * 32) maps_decode_kernel(MapsArgs A, flo
   }
 }
 
-// grid: (requests, query heads); DV threads are enough, any block size works.
+// grid: (requests, query heads); DV threads are enough, any block size works.  The parts' maxima and sums are fetched by
+// one thread each and turned into factors in shared memory; the outputs are then added with independent loads.
 __global__ void __launch_bounds__(128) maps_combine_kernel(MapsArgs A, const float* __restrict__ scratch, int split_keys, int n_splits) {
   __shared__ float red[33];
+  __shared__ float factor_s[MAPS][MAX_SPLITS * WARPS];
+  __shared__ float coef_s[MAPS];
   co_pdl_launch_dependents();
   co_pdl_wait();
   const int r = blockIdx.x, h = blockIdx.y;
@@ -459,21 +462,43 @@ __global__ void __launch_bounds__(128) maps_combine_kernel(MapsArgs A, const flo
   if (q_len != 1) return;
   const int p = A.kv_lens[r] - 1, f = first_visible(p, A.window, A.chunk);
   const int n_parts = (p / split_keys - f / split_keys + 1) * WARPS;
+  const float* base = scratch + ((size_t)r * A.nh + h) * MAPS * (n_splits * WARPS) * (DV + 2);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp < MAPS) {                       // a warp per map: maxima and sums of its parts, merged in a fixed tree
+    const float* parts = base + (size_t)warp * (n_splits * WARPS) * (DV + 2);
+    float m[(MAX_SPLITS * WARPS + 31) / 32], l[(MAX_SPLITS * WARPS + 31) / 32];
+    float M = A.sink ? 0.f : -INFINITY;
+#pragma unroll
+    for (int k = 0; k < (MAX_SPLITS * WARPS + 31) / 32; ++k) {
+      const int i = lane + 32 * k;
+      m[k] = i < n_parts ? parts[i * (DV + 2) + DV] : -INFINITY;
+      l[k] = i < n_parts ? parts[i * (DV + 2) + DV + 1] : 0.f;
+      M = fmaxf(M, m[k]);
+    }
+    M = co_warp_max(M);
+    float L = 0.f;
+#pragma unroll
+    for (int k = 0; k < (MAX_SPLITS * WARPS + 31) / 32; ++k) {
+      const int i = lane + 32 * k;
+      const float fac = ex2(m[k] - M);                    // 0 for a part that saw no key
+      if (i < n_parts) factor_s[warp][i] = fac;
+      L += l[k] * fac;
+    }
+    L = co_warp_sum(L) + (A.sink ? ex2(-M) : 0.f);
+    if (lane == 0) coef_s[warp] = (warp == 0 ? 1.0f : -A.lambda) / L;
+  }
+  __syncthreads();
   float acc[(DV + 127) / 128];
 #pragma unroll
   for (int i = 0; i < (DV + 127) / 128; ++i) acc[i] = 0.f;
   for (int m = 0; m < MAPS; ++m) {
-    const float* parts = scratch + (((size_t)r * A.nh + h) * MAPS + m) * (n_splits * WARPS) * (DV + 2);
-    float M = A.sink ? 0.f : -INFINITY;
-    for (int i = 0; i < n_parts; ++i) M = fmaxf(M, parts[i * (DV + 2) + DV]);
-    float L = A.sink ? ex2(-M) : 0.f;
-    for (int i = 0; i < n_parts; ++i) L += parts[i * (DV + 2) + DV + 1] * ex2(parts[i * (DV + 2) + DV] - M);
-    const float coef = (m == 0 ? 1.0f : -A.lambda) / L;
+    const float* parts = base + (size_t)m * (n_splits * WARPS) * (DV + 2);
     int n = 0;
     for (int d = threadIdx.x; d < DV; d += blockDim.x, ++n) {
       float a = 0.f;
-      for (int i = 0; i < n_parts; ++i) a += parts[i * (DV + 2) + d] * ex2(parts[i * (DV + 2) + DV] - M);
-      acc[n] += coef * a;
+#pragma unroll 8
+      for (int i = 0; i < n_parts; ++i) a = fmaf(parts[i * (DV + 2) + d], factor_s[m][i], a);
+      acc[n] = fmaf(coef_s[m], a, acc[n]);
     }
   }
   float factor = A.out_scale;
@@ -551,7 +576,7 @@ CO_EXPORT int coheryn_attention_maps_bf16(const void* q, long ldq, void* out, lo
     if (smem > 48 * 1024) cudaFuncSetAttribute(maps_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     co_launch(maps_decode_kernel, dim3(B, nkv, n_splits), dim3(WARPS * 32), smem, stream, A, scratch, split_keys, n_splits);
     CO_CHECK_LAUNCH("maps_decode");
-    co_launch(maps_combine_kernel, dim3(B, nh), dim3(DV >= 128 ? 128 : (DV + 31) / 32 * 32), 0, stream, A, (const float*)scratch, split_keys, n_splits);
+    co_launch(maps_combine_kernel, dim3(B, nh), dim3(DV >= 128 ? 128 : (DV > 32 ? (DV + 31) / 32 * 32 : 64)), 0, stream, A, (const float*)scratch, split_keys, n_splits);
     CO_CHECK_LAUNCH("maps_combine");
   }
   return 0;

@@ -757,28 +757,41 @@ add_normed_rmsnorm_vec_kernel(float* __restrict__ resid, const float* __restrict
   float sy[1] = {0.f};
 #pragma unroll
   for (int i = 0; i < VEC; ++i) sy[0] += y[i].x * y[i].x + y[i].y * y[i].y + y[i].z * y[i].z + y[i].w * y[i].w;
+  float* x = resid + src * H;
+  // the stream and the weight of the summand's norm are requested before the reduction that their use waits for
+  float4 xe[VEC], pe[VEC];
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int j = threadIdx.x + i * 256;
+    xe[i] = j < H4 ? reinterpret_cast<const float4*>(x)[j] : zero;
+    pe[i] = j < H4 ? load4_any(post_w, post_dtype, j) : zero;
+  }
   block_sum_n<1>(sy, scratch[1]);
   const float ps = 1.0f / sqrtf(sy[0] * invH + eps);
-  float* x = resid + src * H;
   float sx[1] = {0.f};
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
     const int j = threadIdx.x + i * 256;
     if (j < H4) {
-      const float4 xv = reinterpret_cast<const float4*>(x)[j], pw = load4_any(post_w, post_dtype, j);
+      const float4 xv = xe[i], pw = pe[i];
       y[i] = make_float4(xv.x + (y[i].x * ps) * pw.x, xv.y + (y[i].y * ps) * pw.y, xv.z + (y[i].z * ps) * pw.z, xv.w + (y[i].w * ps) * pw.w);
       if (update) reinterpret_cast<float4*>(x)[j] = y[i];
       sx[0] += y[i].x * y[i].x + y[i].y * y[i].y + y[i].z * y[i].z + y[i].w * y[i].w;
     }
   }
   if (!w) return;
+#pragma unroll
+  for (int i = 0; i < VEC; ++i) {
+    const int j = threadIdx.x + i * 256;
+    pe[i] = j < H4 ? load4_any(w, w_dtype, j) : zero;
+  }
   block_sum_n<1>(sx, scratch[2]);
   const float xs = 1.0f / sqrtf(sx[0] * invH + eps);
 #pragma unroll
   for (int i = 0; i < VEC; ++i) {
     const int j = threadIdx.x + i * 256;
     if (j < H4) {
-      const float4 wv = load4_any(w, w_dtype, j);
+      const float4 wv = pe[i];
       store4(out + (size_t)r * H, (size_t)j, make_float4((y[i].x * xs) * wv.x, (y[i].y * xs) * wv.y, (y[i].z * xs) * wv.z, (y[i].w * xs) * wv.w));
     }
   }

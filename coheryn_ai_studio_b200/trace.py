@@ -59,7 +59,8 @@ def main(argv=None) -> int:
     cache = CacheManager(model.cache_requirements(), [e.cache_from for e in model.spec.schedule],
                          parse_dtype(args.dtype), torch.device(args.device), page_size=args.page_size,
                          num_pages=num_pages, max_requests=args.max_requests, prefix_reuse=False)
-    runner = StepRunner(model, cache)
+    # no request can grow beyond the pool, and the decode kernels cut their work by the longest context they may meet
+    runner = StepRunner(model, cache, graph_max_kv_len=min(model.spec.max_positions, num_pages * args.page_size))
 
     for line in sys.stdin:
         line = line.strip()
