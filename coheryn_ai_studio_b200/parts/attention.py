@@ -307,8 +307,9 @@ class MapsAttention(Mixer):
     def output_weights(self):
         return [self.w_o]
 
-    def forward_open(self, x: torch.Tensor, step: StepContext, cache: LayerCache, outs) -> None:
-        """The heads' outputs in front of the output product into ``outs[0]`` ([T, heads * dv], rows may be strided)."""
+    def _queries(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+        """The projections of ``x``; queries (and, with projections of its own, keys) normalised and rotated; keys and
+        values of every row written to the cache.  Returns q [T, heads * maps * dk] in the compute dtype."""
         Attention._check(cache)
         if cache.writes != self.own_kv:
             raise ValueError("an attention with key and value projections writes its cache; one without reads another's")
@@ -317,13 +318,20 @@ class MapsAttention(Mixer):
         proj = ops.linear(x, self.w_qkv, out_dtype=torch.float32)
         pos = self.position
         rot = pos.rotary_dim if pos is not None else 0
-        q = ops.unit_norm_rope_kv_write(
+        return ops.unit_norm_rope_kv_write(
             proj[:, :nq], proj[:, nq:nq + nk] if self.own_kv else None, proj[:, nq + nk:] if self.own_kv else None,
             self.q_norm, self.k_norm, self.eps, step.positions, pos.frequency_pairs() if pos is not None else None, rot,
             pos.amplitude if pos is not None else 1.0, step.slots[cache.group] if self.own_kv else None, cache.k, cache.v,
             H * M, G * M, G, dk, dv, cache.page_size, self.runtime.dtype)
-        ops.attention_maps(q, outs[0], cache.k, cache.v, step, cache.group, H, G, dk, dv, M, cache.page_size, self.window,
-                           self.chunk, self.sink, self.scale, self.lam, self.head_norm, self.eps, self.out_factor)
+
+    def _attend(self, q: torch.Tensor, out: torch.Tensor, step: StepContext, cache: LayerCache) -> None:
+        ops.attention_maps(q, out, cache.k, cache.v, step, cache.group, self.num_heads, self.num_kv_heads, self.dk, self.dv,
+                           self.maps, cache.page_size, self.window, self.chunk, self.sink, self.scale, self.lam, self.head_norm,
+                           self.eps, self.out_factor)
+
+    def forward_open(self, x: torch.Tensor, step: StepContext, cache: LayerCache, outs) -> None:
+        """The heads' outputs in front of the output product into ``outs[0]`` ([T, heads * dv], rows may be strided)."""
+        self._attend(self._queries(x, step, cache), outs[0], step, cache)
 
     def forward_into(self, x: torch.Tensor, step: StepContext, cache: LayerCache, out: torch.Tensor) -> None:
         o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
@@ -333,6 +341,25 @@ class MapsAttention(Mixer):
     def forward(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
         o = torch.empty((x.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
         self.forward_open(x, step, cache, [o])
+        return ops.linear(o, self.w_o, out_dtype=self.out_dtype, partial_ok=self.partial_output)
+
+    supports_tail = True
+
+    def forward_tail(self, x: torch.Tensor, step: StepContext, cache: LayerCache) -> Optional[torch.Tensor]:
+        """Keys and values of every row go to the cache; only the wanted rows attend (each as a one-token request of
+        ``step.tail``).  An attention that reads another's cache makes the wanted rows' queries only."""
+        rows, tail = step.tail_rows, step.tail
+        if self.own_kv:
+            q = self._queries(x, step, cache)
+            if not tail.num_tokens:
+                return None
+            q = ops.gather_rows(q, rows)
+        else:
+            if not tail.num_tokens:
+                return None
+            q = self._queries(ops.gather_rows(x, rows), tail, cache)
+        o = torch.empty((q.shape[0], self.num_heads * self.dv), dtype=self.runtime.dtype, device=x.device)
+        self._attend(q, o, tail, cache)
         return ops.linear(o, self.w_o, out_dtype=self.out_dtype, partial_ok=self.partial_output)
 
 

@@ -155,6 +155,26 @@ class SandwichResidual(Arrangement):
             delta = PostNormed(self.feed_forward.forward(h, step), post.weight, post.eps)
         return residual, delta
 
+    @property
+    def supports_tail(self):
+        return self.mixer.supports_tail
+
+    def forward_tail(self, residual, delta, step, cache):
+        """The mixer updates its cache for all rows; its output, the feed-forward and both following norms run for the
+        wanted rows only."""
+        h = self.mixer_norm.forward(residual, delta)
+        post = self.mixer_post_norm
+        mixed = self.mixer.forward_tail(h, step, cache)
+        if mixed is None:
+            return None, None
+        kept = ops.gather_rows(residual, step.tail_rows)
+        delta = PostNormed(mixed, post.weight, post.eps)
+        if self.feed_forward is not None:
+            h = self.feed_forward_norm.forward(kept, delta)
+            post = self.feed_forward_post_norm
+            delta = PostNormed(self.feed_forward.forward(h, step.tail), post.weight, post.eps)
+        return kept, delta
+
 
 register_arrangement("sandwich_residual", SandwichResidual)
 register_arrangement("prenorm_residual", PreNormResidual)

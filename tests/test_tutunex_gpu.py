@@ -227,6 +227,35 @@ def test_a_key_that_stands_out_at_every_edge(simple, dk, dv, maps, chunk, page):
                 assert np.abs(outside - v[marked].reshape(G, dv)[0]).max() > 0.3, (marked, "a row of the next chunk saw the key")
 
 
+@pytest.mark.parametrize("simple", [False, True])
+@pytest.mark.parametrize("dk,dv,sink,page", [(32, 32, True, 16), (64, 16, False, 8)])
+def test_a_far_key_among_hundreds_without_chunks(simple, dk, dv, sink, page):
+    """No chunks: every earlier position is seen.  One of the first keys of 420 stands out; rows hundreds of positions later
+    return its value, in a prompt's portion (several row tiles and key tiles away), in a second portion, and decoded alone
+    (several splits away)."""
+    from coheryn_ai_studio_b200 import ops
+    rng = np.random.default_rng(dk)
+    heads, G, n = 4, 2, 420
+    for marked in (0, 5, 17):
+        q, k = rng.normal(size=(n, heads, dk)) * 0.1, rng.normal(size=(n, G, dk)) * 0.1
+        v = bf(rng.normal(size=(n, G * dv)))
+        q[:, :, 1] = 8.0
+        k[marked, :, 1] = 8.0
+        q, k = bf(q.reshape(n, -1)), bf(k.reshape(n, -1))
+        want = plain_maps(q, k, v, heads, G, dk, dv, 1, 1.0, 0.0, None, sink, False, 1e-5, 1.0)
+        cache = Paged([n], G, dk, dv, page, torch.bfloat16, seed=marked)
+        got, at = [], 0
+        for portion in (300, 110, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1):
+            got.append(write_and_attend(cache, cache.step([(0, at, portion)]), q[at:at + portion], k[at:at + portion], v[at:at + portion],
+                                        heads, dk, 1, ops, simple=simple, sink=sink))
+            at += portion
+        got = np.concatenate(got)
+        assert at == n and np.abs(got - want).max() < 0.03, marked
+        value = v[marked].reshape(G, dv)
+        for row in (marked, 299, 300, 409, 410, 419):
+            assert np.abs(got[row].reshape(heads, dv) - np.repeat(value, heads // G, axis=0)).max() < 0.03, (marked, row)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_the_sink_takes_weight_and_carries_no_value(dtype):
     """Scores far below zero: with the sink nearly all weight goes to it and the output nearly vanishes; without it the
@@ -447,6 +476,32 @@ def test_batched_rows_equal_the_rows_of_each_request_alone(dtype, folders, model
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_few_wanted_rows_take_the_last_layers_shortcut(name, dtype, folders, models):
+    """Steps that want few rows (or none) run the last layer's attention, feed-forward and norms for those rows only (T1:
+    a last layer that reads another layer's keys and values; T2, T3: one that writes its own): the logits equal the plain
+    implementation's, the cache that later steps read is complete, and switching the shortcut off changes nothing beyond
+    rounding."""
+    n = 131
+    seq, other = tc.prompt(33, n, vocab(name)), tc.prompt(34, 40, vocab(name))
+    runs = {}
+    for shortcut in (True, False):
+        r = tc.noisy_replay(folders[name], dtype, 256, models(name, dtype))
+        r.runner.tail_shortcut = shortcut
+        r.step([("r", seq[:30], [])])                                   # nothing wanted
+        r.step([("r", seq[30:60], [29, 3]), ("o", other[:20], [19])])    # few rows, out of order, two requests
+        r.step([("r", seq[60:n - 5], [0]), ("o", other[20:], [])])
+        r.step([("r", seq[n - 5:], list(range(5)))])                     # everything wanted: no shortcut
+        assert set(k for k in r.rows if k[0] == "r") == {("r", p) for p in [59, 33, 60] + list(range(n - 5, n))}
+        tc.check_rows(r.rows, folders[name], {"r": seq, "o": other}, dtype, f"shortcut {shortcut}")
+        runs[shortcut] = r.rows
+    assert models(name, dtype).layers[-1].supports_tail
+    for key, row in runs[True].items():
+        d = np.abs(row - runs[False][key]).max()
+        assert d <= (1e-4 if dtype == "float32" else 0.08 * np.std(row)), (key, d)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_tensor_core_attention_equals_the_float32_arithmetic_one_in_a_model(dtype, folders, models):
     """The same steps with the tensor-core kernels switched off: rows agree within rounding (bfloat16), and float32
     never takes them."""
@@ -514,6 +569,39 @@ def test_trace_program_replays_a_schedule(folders, tmp_path):
     got2 = np.fromfile(out / "2.f32", dtype="<f4").reshape(1, V)
     rows = {("a", 0): got0[0], ("a", 24): got0[1], ("b", 11): got1[0], ("a", 39): got2[0]}
     tc.check_rows(rows, folders[name], {"a": a, "b": b}, "float32", "trace")
+
+
+def test_command_line_runs_and_traces_the_design(folders):
+    """`coheryn run` (greedy tokens) and `coheryn trace` (every layer's output and the logits per position) on a folder of
+    this design, and the Python entry point, against the plain implementation."""
+    import json, os, subprocess, sys
+    from coheryn_ai_studio_b200 import api
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    name = "T1"
+    p = tc.prompt(85, 27, vocab(name))
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "coheryn"), "run", folders[name], "--tokens", ",".join(map(str, p)),
+                        "--max-tokens", "5", "--context", "64", "--dtype", "float32", "--stream"], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    got = [int(t) for t in r.stdout.split()]
+    ids = list(p)
+    for tok in got:
+        assert tok == int(np.argmax(tc.plain_rows(folders[name], ids)[-1]))
+        ids.append(tok)
+    assert api.generate(folders[name], [p], max_tokens=5, context=64, dtype="float32")[0]["token_ids"] == got
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "coheryn"), "trace", folders[name], "--tokens", ",".join(map(str, p)),
+                        "--context", "64", "--dtype", "float32"], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    config, w = tc.read_model(folders[name])
+    layers = []
+    ref = plain.forward(config, w, p, layers)
+    assert len(lines) == len(p) * (len(layers) + 1)
+    for l in lines:
+        want = ref[l["position"]] if l["name"] == "logits" else layers[int(l["name"].split(".")[1])][l["position"]]
+        assert np.abs(np.asarray(l["values"], np.float64) - want).max() <= 2e-4 * max(1.0, float(np.abs(want).max())), l["name"]
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "coheryn"), "models", "inspect", folders[name]], capture_output=True,
+                       text=True, timeout=900)
+    assert r.returncode == 0 and "Tutunex" in r.stdout, r.stderr[-2000:]
 
 
 def test_zz_report():
